@@ -3,5 +3,6 @@ from .engine_config import EngineConfig
 from .qwen3 import Qwen3Config
 from .rimopel import RimopelConfig
 from .nagavik import NagavikConfig
+from .fifudra import FifudraConfig
 
-__all__ = ["ConfigError", "ModelConfig", "EngineConfig", "Qwen3Config", "RimopelConfig", "NagavikConfig", "load_config_dict"]
+__all__ = ["ConfigError", "ModelConfig", "EngineConfig", "Qwen3Config", "RimopelConfig", "NagavikConfig", "FifudraConfig", "load_config_dict"]

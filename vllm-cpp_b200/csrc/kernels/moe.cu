@@ -93,6 +93,88 @@ __global__ void moe_route_kernel(Rows logits, const int* __restrict__ q_start, c
         for (int k = lane; k < top; k += 32) sel_w[(size_t)t * top + k] /= denom;
 }
 
+// The same for routers that choose by a corrected score among the experts of the best groups: s = sigmoid(z); the choice
+// score is s + correction; the E experts form `n_groups` equal groups of neighbours, a group's score is the sum of its
+// two largest choice scores, and only experts of the `keep` best groups can be chosen (the others count as minus
+// infinity, so a negative choice score inside a kept group still beats them); the `top` largest choice scores win
+// (the lowest index on a tie); a chosen expert's weight is s * weight_scale, without the correction, not renormalised.
+__global__ void moe_route_grouped_kernel(Rows logits, const float* __restrict__ correction, int n_groups, int keep,
+                                         float weight_scale, const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                         int n_entries, int T, int E, int top, int* __restrict__ sel_e,
+                                         float* __restrict__ sel_w) {
+    extern __shared__ float zs[];   // [warps][2 E + n_groups]
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= T) return;
+    if (entry_of_row(q_start, q_len, n_entries, t) < 0) {
+        for (int k = lane; k < top; k += 32) sel_e[(size_t)t * top + k] = -1;
+        return;
+    }
+    float* s = zs + (size_t)warp * (2 * E + n_groups);
+    float* c = s + E;
+    float* gs = c + E;
+    for (int e = lane; e < E; e += 32) {
+        const float v = 1.f / (1.f + expf(-rows_at(logits, t, e)));
+        s[e] = v;
+        c[e] = v + (correction != nullptr ? correction[e] : 0.f);
+    }
+    __syncwarp();
+    if (n_groups > 1 && keep < n_groups) {
+        const int per = E / n_groups;
+        for (int g = lane; g < n_groups; g += 32) {
+            float a = -CUDART_INF_F, b = -CUDART_INF_F;     // the two largest
+            for (int i = 0; i < per; ++i) {
+                const float v = c[g * per + i];
+                if (v > a) { b = a; a = v; }
+                else if (v > b) b = v;
+            }
+            gs[g] = per > 1 ? a + b : a;
+        }
+        __syncwarp();
+        // the `keep` best groups are marked by NaN-free flags: a kept group's score becomes +inf
+        for (int k = 0; k < keep; ++k) {
+            float best = -CUDART_INF_F;
+            int at = 0x7fffffff;
+            for (int g = lane; g < n_groups; g += 32) {
+                const float v = gs[g];
+                if (v != CUDART_INF_F && (v > best || (v == best && g < at))) { best = v; at = g; }
+            }
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                if (oa != 0x7fffffff && (at == 0x7fffffff || ob > best || (ob == best && oa < at))) { best = ob; at = oa; }
+            }
+            if (lane == 0 && at != 0x7fffffff) gs[at] = CUDART_INF_F;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32)
+            if (gs[e / per] != CUDART_INF_F) c[e] = -CUDART_INF_F;
+        __syncwarp();
+    }
+    for (int k = 0; k < top; ++k) {
+        float best = -CUDART_INF_F;
+        int at = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = c[e];
+            if (v != -CUDART_INF_F && (v > best || (v == best && e < at))) { best = v; at = e; }
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (oa != 0x7fffffff && (at == 0x7fffffff || ob > best || (ob == best && oa < at))) { best = ob; at = oa; }
+        }
+        if (lane == 0) {
+            // (fewer allowed experts than `top` cannot happen for a well-formed router; the choice then names none)
+            sel_e[(size_t)t * top + k] = at == 0x7fffffff ? -1 : at;
+            sel_w[(size_t)t * top + k] = at == 0x7fffffff ? 0.f : s[at] * weight_scale;
+            if (at != 0x7fffffff) c[at] = -CUDART_INF_F;
+        }
+        __syncwarp();
+    }
+}
+
 // one block: counts, padded offsets, the tiles' experts, then every pair's place
 __global__ void moe_group_kernel(const int* __restrict__ sel_e, int A, int E, int tiles_cap, int BM, int* __restrict__ pos_of,
                                  int* __restrict__ src_of, int* __restrict__ tile_expert) {
@@ -310,6 +392,28 @@ VCB_API int vcb_moe_route(const float* logits, int S, long long s_stride, long l
     launch_pdl(moe_route_kernel, dim3((T + warps - 1) / warps), dim3(32 * warps), smem, stream,
                Rows{logits, S < 1 ? 1 : S, s_stride, ld}, q_start, q_len, n_entries, T, E, top, softmax_weights, sel_e, sel_w);
     VCB_CHECK_LAUNCH("moe_route");
+    return 0;
+}
+
+// The router of grouped experts with a corrected choice score (see moe_route_grouped_kernel).  correction [E] or null;
+// n_groups divides E; keep of them can be chosen from (n_groups <= 1 or keep >= n_groups: all experts are open).
+VCB_API int vcb_moe_route_grouped(const float* logits, int S, long long s_stride, long long ld, const float* correction,
+                                  int n_groups, int keep, float weight_scale, const int* q_start, const int* q_len,
+                                  int n_entries, int T, int E, int top, int* sel_e, float* sel_w, cudaStream_t stream) {
+    if (T == 0) return 0;
+    VCB_CHECK_ARG(E >= 1 && top >= 1 && top <= E, "moe_route_grouped: %d of %d experts", top, E);
+    if (n_groups < 1) n_groups = 1;
+    VCB_CHECK_ARG(E % n_groups == 0, "moe_route_grouped: %d experts in %d equal groups", E, n_groups);
+    VCB_CHECK_ARG(n_groups == 1 || keep >= 1, "moe_route_grouped: %d groups kept", keep);
+    VCB_CHECK_ARG(n_groups == 1 || keep >= n_groups || (long long)keep * (E / n_groups) >= top,
+                  "moe_route_grouped: %d groups of %d experts cannot give %d choices", keep, E / n_groups, top);
+    const int warps = 4;
+    const size_t smem = (size_t)warps * (2 * E + n_groups) * sizeof(float);
+    VCB_CHECK_ARG(smem <= 48 * 1024, "moe_route_grouped: %d experts are more than the kernel's shared memory holds", E);
+    launch_pdl(moe_route_grouped_kernel, dim3((T + warps - 1) / warps), dim3(32 * warps), smem, stream,
+               Rows{logits, S < 1 ? 1 : S, s_stride, ld}, correction, n_groups, keep, weight_scale, q_start, q_len, n_entries, T, E,
+               top, sel_e, sel_w);
+    VCB_CHECK_LAUNCH("moe_route_grouped");
     return 0;
 }
 

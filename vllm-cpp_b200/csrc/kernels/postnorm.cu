@@ -89,10 +89,16 @@ __global__ void embed_scaled_pos_kernel(const void* __restrict__ table, int tabl
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
-    int id = ids[t], p = positions[t];
+    int id = ids[t], p = pos_table != nullptr ? positions[t] : 0;
     if (id < 0 || id >= V) {
         if (threadIdx.x == 0 && status != nullptr) atomicOr(status, VCB_STATUS_BAD_TOKEN);
         id = 0;
+    }
+    if (pos_table == nullptr) {
+        // no position vectors: the scaled row alone
+        for (int c = threadIdx.x; c < H; c += blockDim.x)
+            out[(size_t)t * H + c] = load_as_f32(table, table_dtype, (size_t)id * H + c) * scale;
+        return;
     }
     if (p < 0 || p >= P) {
         if (threadIdx.x == 0 && status != nullptr) atomicOr(status, VCB_STATUS_BAD_POSITION);
@@ -307,7 +313,7 @@ VCB_API int vcb_embed_scaled_pos(const void* table, int table_dtype, const int* 
                                  const void* pos_table, int pos_dtype, float scale, float* out, int T, int H, int V, int P,
                                  int* status, cudaStream_t stream) {
     if (T == 0) return 0;
-    VCB_CHECK_ARG(H > 0 && V > 0 && P > 0, "embed_scaled_pos: bad sizes H=%d V=%d P=%d", H, V, P);
+    VCB_CHECK_ARG(H > 0 && V > 0 && (P > 0 || pos_table == nullptr), "embed_scaled_pos: bad sizes H=%d V=%d P=%d", H, V, P);
     launch_pdl(embed_scaled_pos_kernel, dim3(T), dim3(256), 0, stream, table, table_dtype, ids, positions, pos_table, pos_dtype,
                scale, out, H, V, P, status);
     VCB_CHECK_LAUNCH("embed_scaled_pos");

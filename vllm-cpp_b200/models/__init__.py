@@ -9,6 +9,7 @@ from ..registry import architecture_of, get_architecture
 from . import qwen3  # registers Qwen3ForCausalLM
 from . import rimopel  # registers Rimopel
 from . import nagavik  # registers Nagavik
+from . import fifudra  # registers Fifudra
 from .decoder import DecoderModel
 
 

@@ -80,6 +80,14 @@ def _declare(L):
         "vcb_ssm_scan": [P, I, LL, LL, I, P, I, LL, P, P, P, P, LL, P, P, P, I, I, I, I, I, I, I, I, P, P, P, P],
         "vcb_gated_group_norm": [P, P, I, LL, LL, P, F, P, P, I, I, I, I, P, I, P],
         "vcb_moe_route": [P, I, LL, LL, P, P, I, I, I, I, I, P, P, P],
+        "vcb_hyper_mix_norm": [P, P, P, I, LL, LL, P, P, P, P, F, P, I, P, I, I, I, I, P],
+        "vcb_token_shift": [P, P, P, LL, P, P, P, I, I, I, P, I, P],
+        "vcb_latent_norm_rope_store": [P, I, LL, LL, P, P, F, P, P, F, P, P, P, LL, I, I, I, I, I, I, I, P, P],
+        "vcb_head_linear": [P, I, I, LL, LL, I, I, P, I, P, I, LL, I, I, I, I, I, I, P],
+        "vcb_rope_rows": [P, I, LL, LL, I, I, P, P, F, P, I, LL, I, I, I, I, I, I, P],
+        "vcb_matrix_rnn": [I, P, I, LL, LL, P, LL, I, I, I, I, I, P, P, P, P, P, LL, P, P, P, I, I, I, I, I, P, P],
+        "vcb_head_norm_gate": [P, P, I, LL, LL, I, P, F, P, P, I, I, I, I, P, I, P],
+        "vcb_moe_route_grouped": [P, I, LL, LL, P, I, I, F, P, P, I, I, I, I, P, P, P],
         "vcb_moe_group": [P, I, I, I, I, P, P, P, P],
         "vcb_moe_gather": [P, LL, I, P, P, I, I, I, P, P],
         "vcb_gemm_bf16_grouped": [P, P, P, I, I, I, I, I, I, LL, LL, LL, P, I, P, P],
@@ -554,13 +562,18 @@ def bias_act(x, out, kind: str, bias=None):
 
 
 def embed_scaled_pos(table, ids, positions, pos_table, scale, out, status):
-    """out[t] = scale * table[ids[t]] + pos_table[positions[t]]."""
-    _need(table, "table"); _need(pos_table, "pos_table"); _need(ids, "ids", torch.int32)
-    _need(positions, "positions", torch.int32); _need(out, "out", torch.float32)
+    """out[t] = scale * table[ids[t]] + pos_table[positions[t]] (32-bit); ``pos_table`` None: the scaled row alone."""
+    _need(table, "table"); _need(ids, "ids", torch.int32); _need(out, "out", torch.float32)
     T, H = out.shape
-    assert table.shape[1] == H and pos_table.shape[1] == H and ids.numel() >= T and positions.numel() >= T
-    _call("vcb_embed_scaled_pos", _p(table), _dt(table), _p(ids), _p(positions), _p(pos_table), _dt(pos_table), float(scale),
-          _p(out), T, H, table.shape[0], pos_table.shape[0], _p(status), _stream())
+    assert table.shape[1] == H and ids.numel() >= T
+    P = 0
+    if pos_table is not None:
+        _need(pos_table, "pos_table"); _need(positions, "positions", torch.int32)
+        assert pos_table.shape[1] == H and positions.numel() >= T
+        P = pos_table.shape[0]
+    _call("vcb_embed_scaled_pos", _p(table), _dt(table), _p(ids), _p(positions) if pos_table is not None else None,
+          _p(pos_table), _dt(pos_table) if pos_table is not None else F32, float(scale),
+          _p(out), T, H, table.shape[0], P, _p(status), _stream())
 
 
 def postnorm_add_norm(resid, y, post_weight, eps, q_start, q_len, n_entries, *, y_bias=None, layer_scale=None,
@@ -1012,3 +1025,159 @@ def timeline_end():
                                     sm=-1, tile=tag & 0xFFFFFFFF, block=b * _TL_ROLE_EVERY, grid=0, role=role))
     out.sort(key=lambda d: d["t_ns"])
     return out
+
+
+# -------------------------------------------------------------------------- several residual streams, token shift
+
+
+def hyper_mix_norm(streams, *, init=None, y=None, mix=None, outw=None, inw=None, gain=None, eps=0.0, out=None, rows=None):
+    """One pass over the S residual streams ``streams`` [S, T, W] (32-bit): the write-back of the sublayer before
+    (``y``: 32-bit [T, W] or [Sy, T, W] partial sums; x_r <- sum_s mix[s, r] x_s + outw[r] y, ``mix`` and ``outw`` None:
+    the identity and ones), then the read-out for the one ahead (u = sum_r inw[r] x_r, ``inw`` None: the plain sum) and
+    its norm ``gain`` * u / sqrt(mean(u^2) + eps) into ``out`` [n, W] (32-bit or the compute dtype; ``gain`` None: no
+    read-out).  ``init`` [T, W]: the step's first sublayer -- every stream starts as that row.  ``rows`` (int32): only
+    those rows are read out, and the streams are left as they are."""
+    _need(streams, "streams", torch.float32)
+    S, T, W = streams.shape
+    Sy = ys = ldy = 0
+    if y is not None:
+        Sy, ys, ldy = _rows_in(y, "y")
+        assert y.shape[-1] == W and y.shape[-2] >= T
+    for name, t, n in (("mix", mix, S * S), ("outw", outw, S), ("inw", inw, S), ("gain", gain, W)):
+        if t is not None:
+            _need(t, name, torch.float32); assert t.numel() == n, (name, t.shape, n)
+    if init is not None:
+        _need(init, "init", torch.float32); assert init.shape == (T, W)
+    n = T
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        n = rows.numel()
+    if out is not None:
+        _need(out, "out"); assert out.shape[0] >= n and out.shape[1] == W
+    _call("vcb_hyper_mix_norm", _p(streams), _p(init), _p(y), Sy, ys, ldy, _p(mix), _p(outw), _p(inw), _p(gain), float(eps),
+          _p(out), _dt(out) if out is not None else F32, _p(rows), n, T, W, S, _stream())
+
+
+def token_shift(h, mu, state, q_start, q_len, slots, n_entries, out):
+    """out[t] = h[t] + (h[t-1] - h[t]) * mu per channel over each entry's rows (32-bit ``h`` [T, W]); the row before an
+    entry's first is the request's ``state`` [slots, W] (32-bit), which then takes the entry's last row of ``h``."""
+    _need(h, "h", torch.float32); _need(mu, "mu", torch.float32); _need(state, "state", torch.float32, contiguous=False)
+    _need(out, "out")
+    T, W = h.shape
+    assert mu.numel() == W and out.shape == (T, W) and state.shape[-1] == W and state.stride(-1) == 1
+    _call("vcb_token_shift", _p(h), _p(mu), _p(state), state.stride(0), _p(q_start), _p(q_len), _p(slots), n_entries, T, W,
+          _p(out), _dt(out), _stream())
+
+
+# -------------------------------------------------------------------------- attention through a latent
+
+
+def latent_norm_rope_store(u, q_gain, kv_gain, eps, positions, freq, gain, slot_map, cq_out, pages, page_size, q_rank,
+                           kv_rank, rot, status):
+    """From the stacked down projections ``u`` (32-bit [T, q_rank + kv_rank + rot] or partial sums): the normed query
+    latent to ``cq_out`` [T, q_rank]; the normed key/value latent c and the rotated shared key part into the token's
+    cache row.  A page is one flat row: [page_size, kv_rank + rot] key rows [c | k_rot], then [page_size, kv_rank]
+    value rows c.  ``freq`` [rot / 2] 32-bit; cos and sin are multiplied by ``gain``."""
+    S, ss, ld = _rows_in(u, "u")
+    T = u.shape[-2]
+    assert u.shape[-1] == q_rank + kv_rank + rot and rot % 2 == 0
+    _need(cq_out, "cq_out"); _need(pages, "pages", cq_out.dtype); _need(positions, "positions", torch.int32)
+    _need(slot_map, "slot_map", torch.int32); _need(q_gain, "q_gain", torch.float32); _need(kv_gain, "kv_gain", torch.float32)
+    if rot:
+        _need(freq, "freq", torch.float32); assert freq.numel() == rot // 2
+    assert cq_out.shape == (T, q_rank) and q_gain.numel() == q_rank and kv_gain.numel() == kv_rank
+    assert pages[0].numel() == page_size * (2 * kv_rank + rot), (pages.shape, page_size, kv_rank, rot)
+    _call("vcb_latent_norm_rope_store", _p(u), S, ss, ld, _p(q_gain), _p(kv_gain), float(eps), _p(positions), _p(freq),
+          float(gain), _p(slot_map), _p(cq_out), _p(pages), pages.stride(0), int(page_size), pages.shape[0], int(q_rank),
+          int(kv_rank), int(rot), T, _dt(cq_out), _p(status), _stream())
+
+
+def head_linear(x, m, out, *, heads, n_in, n_out, in_head_stride, in_off=0, out_head_stride, out_off=0):
+    """out[t, h * out_head_stride + out_off + j] = sum_c m[h, j, c] x[t, h * in_head_stride + in_off + c]: every head
+    meets a small matrix of its own.  ``x``: 32-bit [T, C] / [S, T, C] partial sums, or one [T, C] buffer of the compute
+    dtype; ``m`` [heads, n_out, n_in]; sums are 32-bit."""
+    _need(m, "m"); _need(out, "out", contiguous=False)
+    assert m.shape == (heads, n_out, n_in) and out.stride(-1) == 1
+    if x.dtype == torch.float32:
+        S, ss, ld = _rows_in(x, "x")
+    else:
+        _need(x, "x", contiguous=False); assert x.dim() == 2 and x.stride(1) == 1
+        S, ss, ld = 1, 0, x.stride(0)
+    T = x.shape[-2]
+    assert (heads - 1) * in_head_stride + in_off + n_in <= x.shape[-1]
+    assert (heads - 1) * out_head_stride + out_off + n_out <= out.shape[-1] and out.shape[0] >= T
+    _call("vcb_head_linear", _p(x), _dt(x), S, ss, ld, int(in_head_stride), int(in_off), _p(m), _dt(m), _p(out), _dt(out),
+          out.stride(0), int(out_head_stride), int(out_off), T, int(heads), int(n_in), int(n_out), _stream())
+
+
+def rope_rows(x, positions, freq, gain, out, *, heads, dims, width, in_head_stride, in_off=0, out_head_stride, out_off=0):
+    """Copies ``width`` lanes of every head's slice of the 32-bit sums ``x`` into ``out``, the first ``dims`` of them
+    rotated: lane i pairs with lane i + dims/2, the angle is position * freq[i], cos and sin times ``gain``."""
+    S, ss, ld = _rows_in(x, "x")
+    T = x.shape[-2]
+    _need(out, "out", contiguous=False); _need(positions, "positions", torch.int32)
+    if dims:
+        _need(freq, "freq", torch.float32); assert freq.numel() == dims // 2
+    assert out.stride(-1) == 1 and dims % 2 == 0
+    assert (heads - 1) * in_head_stride + in_off + width <= x.shape[-1]
+    assert (heads - 1) * out_head_stride + out_off + width <= out.shape[-1]
+    _call("vcb_rope_rows", _p(x), S, ss, ld, int(in_head_stride), int(in_off), _p(positions), _p(freq), float(gain), _p(out),
+          _dt(out), out.stride(0), int(out_head_stride), int(out_off), T, int(heads), int(dims), int(width), _stream())
+
+
+# -------------------------------------------------------------------------- recurrences with a matrix state per head
+
+
+def matrix_rnn(mode, u, state, q_start, q_len, slots, n_entries, out, *, heads, d, dv, q_col, k_col, v_col, x=None,
+               kv_heads=None, b_col=0, a_col=0, dt_bias=None, rate=None, f_bias=None, lower=None):
+    """A recurrence over each entry's tokens whose state is ``state`` [slots, heads, d, dv] (32-bit), ``out`` [T, heads dv].
+
+    ``mode`` "delta": S <- g S; w = beta (v - S^T k); S <- S + k w^T; o = S^T q.  q, k, v are columns ``q_col``,
+    ``k_col``, ``v_col`` of ``x`` [T, C] (32-bit, convolved and activated; q and k of ``kv_heads`` heads, made unit
+    vectors here, q times d^(-1/2)); beta = sigmoid(u[:, b_col + h]), g = exp(-rate_h softplus(u[:, a_col + h] + dt_bias_h)).
+    ``mode`` "gated": S <- diag(f) S + (1 - f) v^T; o = S^T q with q = silu(u[:, q_col ...]), f = lower + (1 - lower)
+    sigmoid(u[:, k_col ...] + f_bias), v = u[:, v_col ...].  ``u``: the projection's 32-bit sums ([S, T, C] partials)."""
+    S, ss, ld = _rows_in(u, "u")
+    _need(state, "state", torch.float32, contiguous=False); _need(out, "out", torch.float32)
+    assert state.shape[1:] == (heads, d, dv) and state[0].is_contiguous() and out.shape[1] == heads * dv
+    m = {"delta": 0, "gated": 1}[mode]
+    ldx = 0
+    if m == 0:
+        _need(x, "x", torch.float32, contiguous=False); assert x.stride(1) == 1
+        ldx = x.stride(0)
+        for name, t in (("dt_bias", dt_bias), ("rate", rate)):
+            _need(t, name, torch.float32); assert t.numel() == heads
+    else:
+        for name, t in (("f_bias", f_bias), ("lower", lower)):
+            _need(t, name, torch.float32); assert t.numel() == heads * d
+    _call("vcb_matrix_rnn", m, _p(u), S, ss, ld, _p(x), ldx, int(q_col), int(k_col), int(v_col), int(b_col), int(a_col),
+          _p(dt_bias), _p(rate), _p(f_bias), _p(lower), _p(state), state.stride(0), _p(q_start), _p(q_len), _p(slots),
+          n_entries, int(heads), int(kv_heads or heads), int(d), int(dv), _p(out), _stream())
+
+
+def head_norm_gate(o, weight, eps, q_start, q_len, n_entries, heads, dv, out, gate=None, gate_col=0):
+    """out[t, h] = weight * o[t, h] / sqrt(mean(o[t, h]^2) + eps) (* silu(gate[t, gate_col + h dv ...]) with a gate):
+    every head of the 32-bit ``o`` [T, heads dv] by its own root mean square, one gain [dv] for all heads."""
+    _need(o, "o", torch.float32); _need(weight, "weight", torch.float32); _need(out, "out")
+    T = o.shape[0]
+    assert o.shape == (T, heads * dv) and out.shape == o.shape and weight.numel() == dv
+    S = ss = ld = 0
+    if gate is not None:
+        S, ss, ld = _rows_in(gate, "gate")
+        assert gate_col + heads * dv <= gate.shape[-1]
+    _call("vcb_head_norm_gate", _p(o), _p(gate), S, ss, ld, int(gate_col), _p(weight), float(eps), _p(q_start), _p(q_len),
+          n_entries, T, int(heads), int(dv), _p(out), _dt(out), _stream())
+
+
+def moe_route_grouped(logits, correction, n_groups, keep, weight_scale, q_start, q_len, n_entries, top, sel_e, sel_w):
+    """The router that chooses by sigmoid(logit) + ``correction`` among the experts of the ``keep`` best of ``n_groups``
+    equal groups of neighbours (a group's score: the sum of its two largest choice scores; ``n_groups`` <= 1: all
+    experts are open); a chosen expert's weight is sigmoid(logit) * ``weight_scale``."""
+    S, ss, ld = _rows_in(logits, "logits")
+    T, E = logits.shape[-2:]
+    _need(sel_e, "sel_e", torch.int32); _need(sel_w, "sel_w", torch.float32)
+    if correction is not None:
+        _need(correction, "correction", torch.float32); assert correction.numel() == E
+    assert sel_e.numel() == T * top and sel_w.numel() == T * top
+    _call("vcb_moe_route_grouped", _p(logits), S, ss, ld, _p(correction), int(n_groups or 1), int(keep or 0), float(weight_scale),
+          _p(q_start), _p(q_len), n_entries, T, E, int(top), _p(sel_e), _p(sel_w), _stream())

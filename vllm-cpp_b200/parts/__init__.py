@@ -5,7 +5,10 @@ from .base import Block, BuildContext, CacheSpec, FeedForward, Mixer, Norm, Part
 from .block import PreNormBlock
 from .embedding import Embedding, Head, LMHead, PositionalTokenEmbedding, SinusoidalTokenEmbedding, TokenEmbedding
 from .gated_block import GatedPostNormBlock
+from .hyper_block import HyperStreamsBlock
+from .latent_attention import LatentAttention
 from .mamba2 import Mamba2Mixer
+from .matrix_rnn import DeltaRuleMixer, GatedLinearMixer
 from .mlp import DenseMLP, GatedMLP, SwiGLUMLP
 from .moe import RoutedExperts
 from .sandwich_block import SandwichNormBlock
@@ -29,8 +32,12 @@ register_part("mixer", "mamba2", Mamba2Mixer)
 register_part("feed_forward", "gated_mlp", GatedMLP)
 register_part("feed_forward", "routed_experts", RoutedExperts)
 register_part("block", "sandwich_norm", SandwichNormBlock)
+register_part("mixer", "latent_attention", LatentAttention)
+register_part("mixer", "delta_rule", DeltaRuleMixer)
+register_part("mixer", "gated_linear", GatedLinearMixer)
+register_part("block", "hyper_streams", HyperStreamsBlock)
 
 __all__ = ["Block", "BuildContext", "CacheSpec", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding",
            "PreNormBlock", "Embedding", "Head", "LMHead", "TokenEmbedding", "SwiGLUMLP", "DenseMLP", "GatedPostNormBlock",
            "ConvWindowAttention", "SinusoidalTokenEmbedding", "PositionalTokenEmbedding",
-           "Mamba2Mixer", "GatedMLP", "RoutedExperts", "SandwichNormBlock", "RMSNorm", "RotaryEmbedding", "GQAAttention"]
+           "Mamba2Mixer", "LatentAttention", "DeltaRuleMixer", "GatedLinearMixer", "HyperStreamsBlock", "GatedMLP", "RoutedExperts", "SandwichNormBlock", "RMSNorm", "RotaryEmbedding", "GQAAttention"]

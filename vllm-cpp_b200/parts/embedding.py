@@ -40,11 +40,13 @@ class Head(Part):
 
 
 class TokenEmbedding(Embedding):
-    """params: ``tensor`` (checkpoint name of the table), ``vocab_size``, ``hidden_size``."""
+    """params: ``tensor`` (checkpoint name of the table), ``vocab_size``, ``hidden_size``; optional ``scale`` (default 1):
+    a constant on the gathered row (a tied head reads the table itself, without it)."""
 
     def __init__(self, params, prefix, build):
         super().__init__(params, prefix, build)
         self.name, self.vocab, self.hidden = str(params["tensor"]), int(params["vocab_size"]), int(params["hidden_size"])
+        self.scale = float(params.get("scale", 1.0))
         self.table = None
 
     def tensor_specs(self):
@@ -55,7 +57,10 @@ class TokenEmbedding(Embedding):
 
     def forward(self, ids, n_tokens, status):
         out = workspace.empty((n_tokens, self.hidden), torch.float32, ids.device)
-        ops.embed_gather(self.table, ids, out, status)
+        if self.scale != 1.0:
+            ops.embed_scaled_pos(self.table, ids, None, None, self.scale, out, status)
+        else:
+            ops.embed_gather(self.table, ids, out, status)
         return out
 
 

@@ -45,6 +45,55 @@ MMA_ATTENTION = os.environ.get("VLLM_CPP_B200_WINDOW_ATTN_MMA", "1") != "0"
 EXTRAS_ON_TENSOR_CORES = True
 
 
+def paged_attention(ctx, kv, q, out, *, nh, nkv, hd, vd, scale, window=0, keep_first=0, dist_a=None, dist_b=None,
+                    softcap=0.0, slope=None, sink=False):
+    """Scores, softmax and weighted sums of one step over the paged keys and values ``kv``: ``q`` [T, nh * hd] against
+    keys of ``hd`` lanes, values of ``vd`` lanes into ``out`` [T, nh * vd].  Single tokens are cut into key slices and
+    merged, prompt portions into row tiles; bfloat16 with keys and values of 64 or 128 lanes runs on the tensor cores
+    (tcgen05 for prompt portions where the page size allows, mma.sync for decoded tokens), everything else on the
+    plain kernel.  Whoever keeps its keys in pages of this layout calls this (the window attention below; attention
+    over latent rows, whose one KV head's values are the first lanes of its keys)."""
+    x = q
+    # no query reads more keys than the window and the kept first ones: no more key slices than those fill
+    reach = window + keep_first if window else 0
+    # bfloat16 with keys and values of 64 or 128 lanes: the tensor-core kernel; else the plain one
+    extras = dict(softcap=softcap, slope=slope, sink=sink)
+    has_extras = bool(softcap or slope is not None or sink)
+    mma = (MMA_ATTENTION and vd == hd and kv.pages.dim() == 5 and ops.attn_mma_supported(x.dtype, hd)
+           and (EXTRAS_ON_TENSOR_CORES or not has_extras))
+    dec_rows, span_rows = (MMA_DECODE_ROWS, MMA_SPAN_ROWS) if mma else (DECODE_ROWS, SPAN_ROWS)
+    clustered = hd if mma and CLUSTER_MERGE and torch.cuda.is_available() else None
+    group = ctx.groups[kv.group]
+    plan = ctx.plan(("attention", nh, nkv, mma, clustered, reach),
+                    lambda: AttentionPlan(ctx, nh, nkv, dec_rows, span_rows, clustered, max_keys=reach))
+    common = dict(nh=nh, nkv=nkv, hd=hd, window=window, status=ctx.status, table_row=ctx.slots, scale=scale,
+                  keep_first=keep_first, dist_a=dist_a, dist_b=dist_b, **extras)
+    args = (q, out, kv.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len)
+    if plan.n_dec:
+        S = plan.nslices
+        cluster = plan.cluster if mma else 0
+        part_o = part_ml = None
+        if S > 1 and not cluster:
+            part_o = workspace.empty((plan.n_dec * nh * S, vd), torch.float32, x.device)
+            part_ml = workspace.empty((plan.n_dec * nh * S, 2), torch.float32, x.device)
+        if mma:
+            ops.attn_mma(*args, plan.dec_items, plan.n_dec * S, dec_rows, part_o, part_ml,
+                         slice_counters=plan.slice_counters if S > 1 else None, dec_rows=plan.dec_rows, cluster=cluster,
+                         **common)
+        else:
+            ops.attn_window_bias(*args, plan.dec_items, plan.n_dec * S, dec_rows, part_o, part_ml, hd_v=vd, **common)
+            if S > 1:
+                ops.attn_merge(part_o, part_ml, plan.dec_rows, out, plan.n_dec, nh, vd, S)
+    if plan.n_span_items:
+        if mma and TCGEN05_SPANS and ops.attn_tc_supported(x.dtype, hd, kv.pages.shape[3]):
+            ops.attn_tc(*args, plan.span_items, plan.n_span_items, work=plan.span_work, **common)
+        elif mma:
+            ops.attn_mma(*args, plan.span_items, plan.n_span_items, span_rows, None, None, **common)
+        else:
+            ops.attn_window_bias(*args, plan.span_items, plan.n_span_items, span_rows, None, None,
+                                 hd_v=vd, **common)
+
+
 class ConvWindowAttention(Mixer):
     """params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``v_head_dim`` (default head_dim),
     ``scale`` (default 1/sqrt(head_dim)), ``window`` (0: all keys), ``keep_first``, ``conv_taps`` (0: none), ``eps``,
@@ -144,40 +193,7 @@ class ConvWindowAttention(Mixer):
             # (entries of one token were brought up to date by the kernel above)
             ops.conv_state_update(qkv, st, ctx.q_start, ctx.q_len, ctx.slots, ctx.E, bias=self.bias)
         out = workspace.empty((T, nh * vd), x.dtype, x.device)
-        # no query reads more keys than the window and the kept first ones: no more key slices than those fill
-        reach = self.window + self.keep_first if self.window else 0
-        # bfloat16 with keys and values of 64 or 128 lanes: the tensor-core kernel; else the plain one
-        extras = dict(softcap=self.softcap, slope=self.slope, sink=self.sink)
-        has_extras = bool(self.softcap or self.slope is not None or self.sink)
-        mma = (MMA_ATTENTION and vd == hd and kv.pages.dim() == 5 and ops.attn_mma_supported(x.dtype, hd)
-               and (EXTRAS_ON_TENSOR_CORES or not has_extras))
-        dec_rows, span_rows = (MMA_DECODE_ROWS, MMA_SPAN_ROWS) if mma else (DECODE_ROWS, SPAN_ROWS)
-        clustered = hd if mma and CLUSTER_MERGE and torch.cuda.is_available() else None
-        plan = ctx.plan(("attention", nh, nkv, mma, clustered, reach),
-                        lambda: AttentionPlan(ctx, nh, nkv, dec_rows, span_rows, clustered, max_keys=reach))
-        common = dict(nh=nh, nkv=nkv, hd=hd, window=self.window, status=ctx.status, table_row=ctx.slots, scale=self.scale,
-                      keep_first=self.keep_first, dist_a=self.dist_a, dist_b=self.dist_b, **extras)
-        args = (q, out, kv.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len)
-        if plan.n_dec:
-            S = plan.nslices
-            cluster = plan.cluster if mma else 0
-            part_o = part_ml = None
-            if S > 1 and not cluster:
-                part_o = workspace.empty((plan.n_dec * nh * S, vd), torch.float32, x.device)
-                part_ml = workspace.empty((plan.n_dec * nh * S, 2), torch.float32, x.device)
-            if mma:
-                ops.attn_mma(*args, plan.dec_items, plan.n_dec * S, dec_rows, part_o, part_ml,
-                             slice_counters=plan.slice_counters if S > 1 else None, dec_rows=plan.dec_rows, cluster=cluster,
-                             **common)
-            else:
-                ops.attn_window_bias(*args, plan.dec_items, plan.n_dec * S, dec_rows, part_o, part_ml, hd_v=vd, **common)
-                if S > 1:
-                    ops.attn_merge(part_o, part_ml, plan.dec_rows, out, plan.n_dec, nh, vd, S)
-        if plan.n_span_items:
-            if mma and TCGEN05_SPANS and ops.attn_tc_supported(x.dtype, hd, kv.pages.shape[3]):
-                ops.attn_tc(*args, plan.span_items, plan.n_span_items, work=plan.span_work, **common)
-            elif mma:
-                ops.attn_mma(*args, plan.span_items, plan.n_span_items, span_rows, None, None, **common)
-            else:
-                ops.attn_window_bias(*args, plan.span_items, plan.n_span_items, span_rows, None, None, hd_v=vd, **common)
+        paged_attention(ctx, kv, q, out, nh=nh, nkv=nkv, hd=hd, vd=vd, scale=self.scale, window=self.window,
+                        keep_first=self.keep_first, dist_a=self.dist_a, dist_b=self.dist_b, softcap=self.softcap,
+                        slope=self.slope, sink=self.sink)
         return matmul_tn(out, self.w_o, ctx.status, out_dtype=torch.float32, allow_partials=True)

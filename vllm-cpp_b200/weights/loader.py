@@ -30,7 +30,8 @@ class TensorSpec:
     name: str
     shape: tuple
     # "matrix" (operand of a matrix product), "vector" (gains), "bias" (additive terms, convolution taps), "positive"
-    # (rates that must not be negative), "table" (integers); all but the first and last are read with ``vector``
+    # (rates that must not be negative), "unit" (numbers in [0, 1)), "mixing" (a small square matrix near the identity),
+    # "table" (integers); all but the first and last are read with ``vector``
     role: str = "matrix"
     optional: bool = False
     high: int = 0            # role "table": entries lie in [0, high) (what the random-weights mode draws from)

@@ -35,6 +35,11 @@ def _generate(spec: TensorSpec, seed: int, device="cpu") -> torch.Tensor:
         return GAIN_STD * torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
     if spec.role == "positive":   # rates and strengths that must not be negative
         return 0.05 + 0.2 * torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device).abs()
+    if spec.role == "unit":       # lower bounds and shares that lie in [0, 1)
+        return 0.9 * torch.rand(spec.shape, generator=g, dtype=torch.float32, device=device)
+    if spec.role == "mixing":     # a small square matrix that mixes parallel streams: near the identity
+        eye = torch.eye(spec.shape[0], spec.shape[1], dtype=torch.float32, device=device)
+        return eye + GAIN_STD * torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
     if spec.role == "table":
         if spec.high < 1:
             raise ValueError(f"integer table '{spec.name}' does not say what range its entries have (TensorSpec.high)")
