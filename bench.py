@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Benchmark of the engine on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--workloads all|headline|14b|4b|rimopel|nagavik] [--impl reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--workloads all|headline|14b|4b|rimopel|nagavik|fifudra] [--impl reference]
 
 Headline: decode tokens/s of the Qwen3-8B layer sizes (the baseline's third configuration) at batch 8 and context
 4,096, the median of K device-timed steps after W warm-up steps; beside it batch 1 and 64, batch 8 at context 2,176
@@ -590,51 +590,121 @@ NAGAVIK_SIZES = {
 }
 
 
+def nagavik_kinds(z):
+    return ["attention" if i % 3 == 2 else "mamba2" for i in range(z["layers"])]
+
+
+def nagavik_config(z, context):
+    from vllm_cpp_b200.config.nagavik import NagavikAttention, NagavikConfig, NagavikLayer, NagavikMamba2, NagavikMlp
+    attn = NagavikAttention(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5, softcap=50.0)
+    ssm = NagavikMamba2(heads=z["ssm_heads"], vdim=z["ssm_vdim"], state=z["state"], groups=z["groups"], conv=4, norm_groups=z["groups"])
+    mlp = NagavikMlp("moe", ff=z["ff"], experts=z["experts"], top=z["top"], shared_ff=z["shared"])
+    return NagavikConfig(vocab=z["vocab"], width=z["width"], max_positions=context + 4096, norm_eps=1e-5, embedding_scale=1.0,
+                         logit_softcap=30.0,
+                         layers=tuple(NagavikLayer(k, attn if k == "attention" else ssm, mlp) for k in nagavik_kinds(z)))
+
+
+def nagavik_numbers(z, context, T, B):
+    W, H, G, d, L, V = z["width"], z["heads"], z["kv_heads"], z["dim"], z["layers"], z["vocab"]
+    attn_w = (H + 2 * G) * d * W + W * H * d
+    attn_flops = 4.0 * H * d * sum(i + 1 for i in range(T))
+    n_attn = nagavik_kinds(z).count("attention")
+    n_ssm = L - n_attn
+    inner, gn = z["ssm_heads"] * z["ssm_vdim"], z["groups"] * z["state"]
+    ssm_w = (2 * inner + 2 * gn + z["ssm_heads"]) * W + W * inner
+    expert = 2 * z["ff"] * W
+    ff_active = z["top"] * expert + 2 * z["shared"] * W + z["experts"] * W
+    # experts a decode step reads: the distinct ones B tokens choose, in expectation
+    distinct = z["experts"] * (1.0 - (1.0 - z["top"] / z["experts"]) ** B)
+    ff_read = distinct * expert + 2 * z["shared"] * W + z["experts"] * W
+    state_bytes = 2 * 4 * inner * z["state"]       # read and written, 32-bit
+    return dict(weight_bytes=2 * (n_attn * attn_w + n_ssm * ssm_w + L * ff_read + V * W),
+                cache_bytes=n_attn * 2 * G * d * 2 * context + n_ssm * state_bytes,
+                prefill_flops=2.0 * T * (n_attn * attn_w + n_ssm * ssm_w + L * ff_active) + 2.0 * V * W + n_attn * attn_flops
+                              + n_ssm * 6.0 * T * inner * z["state"])
+
+
 def run_nagavik(args, pk, clocks, windows):
     """Nagavik at real layer sizes beside Qwen3 at equal size (see NAGAVIK_SIZES and run_beside)."""
     from vllm_cpp_b200 import Qwen3Config
-    from vllm_cpp_b200.config.nagavik import NagavikAttention, NagavikConfig, NagavikLayer, NagavikMamba2, NagavikMlp
     context, T, B = args.context, PREFILL_TOKENS, args.batch
 
-    def kinds(z):
-        return ["attention" if i % 3 == 2 else "mamba2" for i in range(z["layers"])]
-
     def configs(z):
-        attn = NagavikAttention(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5, softcap=50.0)
-        ssm = NagavikMamba2(heads=z["ssm_heads"], vdim=z["ssm_vdim"], state=z["state"], groups=z["groups"], conv=4, norm_groups=z["groups"])
-        mlp = NagavikMlp("moe", ff=z["ff"], experts=z["experts"], top=z["top"], shared_ff=z["shared"])
-        nag = NagavikConfig(vocab=z["vocab"], width=z["width"], max_positions=context + 4096, norm_eps=1e-5, embedding_scale=1.0,
-                            logit_softcap=30.0,
-                            layers=tuple(NagavikLayer(k, attn if k == "attention" else ssm, mlp) for k in kinds(z)))
         qwen = Qwen3Config(vocab_size=z["vocab"], hidden_size=z["width"], intermediate_size=z["swiglu"], num_hidden_layers=z["layers"],
                            num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["dim"],
                            max_position_embeddings=context + 4096, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
-        return {"nagavik": nag, "qwen3": qwen}
+        return {"nagavik": nagavik_config(z, context), "qwen3": qwen}
 
     def numbers(z, name):
         W, H, G, d, L, V = z["width"], z["heads"], z["kv_heads"], z["dim"], z["layers"], z["vocab"]
-        attn_w = (H + 2 * G) * d * W + W * H * d
-        attn_flops = 4.0 * H * d * sum(i + 1 for i in range(T))
         if name == "qwen3":
+            attn_w = (H + 2 * G) * d * W + W * H * d
             layer = attn_w + 3 * z["swiglu"] * W
             return dict(weight_bytes=2 * (L * layer + V * W), cache_bytes=L * 2 * G * d * 2 * context,
-                        prefill_flops=2.0 * T * L * layer + 2.0 * V * W + L * attn_flops)
-        n_attn = kinds(z).count("attention")
-        n_ssm = L - n_attn
-        inner, gn = z["ssm_heads"] * z["ssm_vdim"], z["groups"] * z["state"]
-        ssm_w = (2 * inner + 2 * gn + z["ssm_heads"]) * W + W * inner
-        expert = 2 * z["ff"] * W
-        ff_active = z["top"] * expert + 2 * z["shared"] * W + z["experts"] * W
-        # experts a decode step reads: the distinct ones B tokens choose, in expectation
-        distinct = z["experts"] * (1.0 - (1.0 - z["top"] / z["experts"]) ** B)
-        ff_read = distinct * expert + 2 * z["shared"] * W + z["experts"] * W
-        state_bytes = 2 * 4 * inner * z["state"]       # read and written, 32-bit
-        return dict(weight_bytes=2 * (n_attn * attn_w + n_ssm * ssm_w + L * ff_read + V * W),
-                    cache_bytes=n_attn * 2 * G * d * 2 * context + n_ssm * state_bytes,
-                    prefill_flops=2.0 * T * (n_attn * attn_w + n_ssm * ssm_w + L * ff_active) + 2.0 * V * W + n_attn * attn_flops
-                                  + n_ssm * 6.0 * T * inner * z["state"])
+                        prefill_flops=2.0 * T * L * layer + 2.0 * V * W + L * 4.0 * H * d * sum(i + 1 for i in range(T)))
+        return nagavik_numbers(z, context, T, B)
 
     return run_beside(args, pk, clocks, windows, "nagavik_beside_qwen3", NAGAVIK_SIZES, configs, numbers)
+
+
+# Fifudra at real layer sizes beside Nagavik, the closest design the engine has (recurrent layers with an attention layer
+# after every two, routed experts on every layer), at equal width, layer count, recurrent state per request and active
+# feed-forward parameters per token: a delta-rule layer, a gated linear layer, an attention layer through a latent, and so
+# on; four residual streams; four of sixteen gated experts chosen within two of four groups.
+FIFUDRA_SIZES = {
+    "w2048": dict(NAGAVIK_SIZES["w2048"], f_heads=16, f_dim=128, f_rot=64, f_vdim=128, q_rank=768, kv_rank=192, r_heads=16, r_kv_heads=8,
+                  r_dim=128, r_vdim=256, f_ff=1024, f_top=4, f_groups=4, f_keep=2, streams=4),
+    "w4096": dict(NAGAVIK_SIZES["w4096"], f_heads=32, f_dim=128, f_rot=64, f_vdim=128, q_rank=1536, kv_rank=192, r_heads=32, r_kv_heads=16,
+                  r_dim=128, r_vdim=256, f_ff=2048, f_top=4, f_groups=4, f_keep=2, streams=4),
+}
+
+
+def run_fifudra(args, pk, clocks, windows):
+    """Fifudra at real layer sizes beside Nagavik at equal size (see FIFUDRA_SIZES and run_beside)."""
+    from vllm_cpp_b200.config.fifudra import (DeltaSpec, FifudraConfig, FifudraLayer, FifudraMlp, Hgrn2Spec, LatentAttentionSpec,
+                                              RotarySpec)
+    context, T, B = args.context, PREFILL_TOKENS, args.batch
+
+    def kinds(z):
+        return [("delta", "hgrn2", "latent_attention")[i % 3] for i in range(z["layers"])]
+
+    def configs(z):
+        mixers = {"delta": DeltaSpec(heads=z["r_heads"], kv_heads=z["r_kv_heads"], dim=z["r_dim"], vdim=z["r_vdim"], conv=4),
+                  "hgrn2": Hgrn2Spec(heads=z["r_heads"], dim=z["r_dim"], vdim=z["r_vdim"]),
+                  "latent_attention": LatentAttentionSpec(
+                      heads=z["f_heads"], dim=z["f_dim"], rot_dim=z["f_rot"], vdim=z["f_vdim"], q_rank=z["q_rank"], kv_rank=z["kv_rank"],
+                      scale=(z["f_dim"] + z["f_rot"]) ** -0.5,
+                      rot=RotarySpec(base=1e6, dims=z["f_rot"], factor=4.0, original=4096.0, fast=32.0, slow=1.0))}
+        mlp = FifudraMlp("moe", ff=z["f_ff"], experts=z["experts"], top=z["f_top"], scale=1.0, groups=z["f_groups"], keep=z["f_keep"])
+        fif = FifudraConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-5, embedding_scale=1.0, streams=z["streams"],
+                            max_positions=context + 4096, layers=tuple(FifudraLayer(k, mixers[k], mlp) for k in kinds(z)))
+        return {"fifudra": fif, "nagavik": nagavik_config(z, context)}
+
+    def numbers(z, name):
+        if name == "nagavik":
+            return nagavik_numbers(z, context, T, B)
+        W, L, V = z["width"], z["layers"], z["vocab"]
+        H, d, r, vd, qr, kr = z["f_heads"], z["f_dim"], z["f_rot"], z["f_vdim"], z["q_rank"], z["kv_rank"]
+        RH, RG, rd, rv = z["r_heads"], z["r_kv_heads"], z["r_dim"], z["r_vdim"]
+        n = {k: kinds(z).count(k) for k in ("delta", "hgrn2", "latent_attention")}
+        lat_w = (qr + kr + r) * W + H * (d + r) * qr + H * d * kr + H * vd * kr + W * H * vd
+        delta_w = (2 * RG * rd + 2 * RH * rv + 2 * RH) * W + W * RH * rv
+        hgrn_w = (2 * RH * rd + RH * rv) * W + W * RH * rv
+        expert = 3 * z["f_ff"] * W
+        ff_active = z["f_top"] * expert + z["experts"] * W
+        distinct = z["experts"] * (1.0 - (1.0 - z["f_top"] / z["experts"]) ** B)
+        ff_read = distinct * expert + z["experts"] * W
+        mixers_w = n["latent_attention"] * lat_w + n["delta"] * delta_w + n["hgrn2"] * hgrn_w
+        state_bytes = 2 * 4 * RH * rd * rv              # read and written, 32-bit
+        keys = sum(i + 1 for i in range(T))
+        return dict(weight_bytes=2 * (mixers_w + L * ff_read + V * W),
+                    # a cached token: the key row [latent | rotated part] and the value row (the latent), 16-bit
+                    cache_bytes=n["latent_attention"] * (2 * kr + r) * 2 * context + (n["delta"] + n["hgrn2"]) * state_bytes,
+                    prefill_flops=2.0 * T * (mixers_w + L * ff_active) + 2.0 * V * W
+                                  + n["latent_attention"] * 2.0 * H * (2 * kr + r) * keys
+                                  + (6.0 * n["delta"] + 4.0 * n["hgrn2"]) * T * RH * rd * rv)
+
+    return run_beside(args, pk, clocks, windows, "fifudra_beside_nagavik", FIFUDRA_SIZES, configs, numbers)
 
 
 def main():
@@ -648,10 +718,11 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--workloads", default="all", choices=["all", "headline", "14b", "4b", "rimopel", "nagavik"],
+    ap.add_argument("--workloads", default="all", choices=["all", "headline", "14b", "4b", "rimopel", "nagavik", "fifudra"],
                     help="headline: the 8B numbers only; 14b / 4b: that workload alone (prints its own JSON line); rimopel, "
-                         "nagavik: that design at real layer sizes beside Qwen3 at equal size, prefill and decode (its own JSON line)")
-    ap.add_argument("--size", default="", help="rimopel, nagavik: one of the workload's sizes only (w2048, w4096)")
+                         "nagavik: that design at real layer sizes beside Qwen3 at equal size, prefill and decode (its own JSON line); "
+                         "fifudra: that design beside Nagavik at equal size, likewise")
+    ap.add_argument("--size", default="", help="rimopel, nagavik, fifudra: one of the workload's sizes only (w2048, w4096)")
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profiling runs)")
     ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill"], help="what to run (profiling runs)")
@@ -673,8 +744,8 @@ def main():
     clocks.start()
     windows = []
     try:
-        if args.workloads in ("14b", "4b", "rimopel", "nagavik"):
-            out = {"14b": run_14b, "4b": run_4b, "rimopel": run_rimopel, "nagavik": run_nagavik}[args.workloads](args, pk, clocks, windows)
+        if args.workloads in ("14b", "4b", "rimopel", "nagavik", "fifudra"):
+            out = {"14b": run_14b, "4b": run_4b, "rimopel": run_rimopel, "nagavik": run_nagavik, "fifudra": run_fifudra}[args.workloads](args, pk, clocks, windows)
             out["clocks"] = clocks.summary(windows)
             print(json.dumps(out))
             return 0

@@ -6,11 +6,20 @@ position and, if asked, the sum of the residual streams after every layer run.
 """
 from __future__ import annotations
 
+import json
 import math
+from pathlib import Path
 
 import torch
 
+from plain_qwen3 import read_safetensors
+
 F64 = torch.float64
+
+
+def read_model(model_dir):
+    model_dir = Path(model_dir)
+    return json.loads((model_dir / "config.json").read_text()), read_safetensors(model_dir / "model.safetensors")
 
 
 def rms_norm(x, w, eps):
@@ -149,28 +158,39 @@ def gated_ff(h, gate, up, down):
     return (silu(h @ gate.T) * (h @ up.T)) @ down.T
 
 
-def route(h, w_router, correction, router):
-    """-> (chosen experts [T, top], their weights [T, top])."""
+def route(h, w_router, correction, router, margins=None):
+    """-> (chosen experts [T, top], their weights [T, top]).  ``margins`` (a list) receives, per call, the smallest gap
+    by which any token's choice was decided: between the last chosen and the first left-out choice score, and between
+    the last kept and the first dropped group."""
     E, top = int(router["experts"]), int(router["top"])
     s = torch.sigmoid(h @ w_router.T)
     choice = s + correction
     groups = router.get("groups")
+    gap = math.inf
     if groups:
         n, keep = int(groups["count"]), int(groups["keep"])
         per = E // n
         grouped = choice.view(-1, n, per)
         score = grouped.topk(min(2, per), -1).values.sum(-1)
         kept = score.topk(keep, -1).indices
+        if keep < n:
+            ranked = score.sort(-1, descending=True).values
+            gap = min(gap, float((ranked[:, keep - 1] - ranked[:, keep]).min()))
         allowed = torch.zeros(choice.shape[0], n, dtype=torch.bool)
         allowed.scatter_(1, kept, True)
         choice = torch.where(allowed[:, :, None].expand(-1, -1, per).reshape(-1, E), choice,
                              torch.full_like(choice, -math.inf))
     chosen = choice.topk(top, -1).indices
-    return chosen, s.gather(1, chosen) * float(router["scale"])
+    if top < E:
+        ranked = choice.sort(-1, descending=True).values
+        gap = min(gap, float((ranked[:, top - 1] - ranked[:, top]).min()))
+    if margins is not None:
+        margins.append(gap)
+    return chosen, s.gather(1, chosen) * float(router.get("scale", 1.0))
 
 
-def routed_ff(h, w, mlp):
-    chosen, weight = route(h, w["router"], w["correction"], mlp["router"])
+def routed_ff(h, w, mlp, margins=None):
+    chosen, weight = route(h, w["router"], w["correction"], mlp["router"], margins)
     out = torch.zeros(h.shape[0], w["e0.down"].shape[0], dtype=F64)
     for t in range(h.shape[0]):
         for e, a in zip(chosen[t].tolist(), weight[t]):
@@ -194,8 +214,9 @@ def sub(tensors, prefix):
     return {k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def forward(cfg, tensors, tokens, want_layers=False):
-    """tokens: a list of ids -> logits [T, vocab] (and [runs, T, W] sums of the streams after every layer run)."""
+def forward(cfg, tensors, tokens, want_layers=False, margins=None):
+    """tokens: a list of ids -> logits [T, vocab] (and [runs, T, W] sums of the streams after every layer run).
+    ``margins``: see ``route``."""
     eps = float(cfg["norm"]["eps"])
     x = tensors["embed"][torch.tensor(tokens)] * float(cfg.get("embedding", {}).get("scale", 1.0))
     n_streams = cfg.get("streams")
@@ -219,7 +240,7 @@ def forward(cfg, tensors, tokens, want_layers=False):
                      else MIXERS[layer["type"]](h, w, layer["mixer"], eps))
             else:
                 w = sub(t, "mlp.")
-                y = gated_ff(h, w["gate"], w["up"], w["down"]) if layer["mlp"]["kind"] == "dense" else routed_ff(h, w, layer["mlp"])
+                y = gated_ff(h, w["gate"], w["up"], w["down"]) if layer["mlp"]["kind"] == "dense" else routed_ff(h, w, layer["mlp"], margins)
             if n_streams:
                 streams = hyper_write(streams, y, t[f"hc{q}.mix"], t[f"hc{q}.out"])
             else:
