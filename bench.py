@@ -652,10 +652,13 @@ def run_nagavik(args, pk, clocks, windows):
 # feed-forward parameters per token: a delta-rule layer, a gated linear layer, an attention layer through a latent, and so
 # on; four residual streams; four of sixteen gated experts chosen within two of four groups.
 FIFUDRA_SIZES = {
-    "w2048": dict(NAGAVIK_SIZES["w2048"], f_heads=16, f_dim=128, f_rot=64, f_vdim=128, q_rank=768, kv_rank=192, r_heads=16, r_kv_heads=8,
+    "w2048": dict(NAGAVIK_SIZES["w2048"], f_heads=16, f_dim=128, f_rot=32, f_vdim=128, q_rank=768, kv_rank=96, r_heads=16, r_kv_heads=8,
                   r_dim=128, r_vdim=256, f_ff=1024, f_top=4, f_groups=4, f_keep=2, streams=4),
-    "w4096": dict(NAGAVIK_SIZES["w4096"], f_heads=32, f_dim=128, f_rot=64, f_vdim=128, q_rank=1536, kv_rank=192, r_heads=32, r_kv_heads=16,
+    "w4096": dict(NAGAVIK_SIZES["w4096"], f_heads=32, f_dim=128, f_rot=32, f_vdim=128, q_rank=1536, kv_rank=96, r_heads=32, r_kv_heads=16,
                   r_dim=128, r_vdim=256, f_ff=2048, f_top=4, f_groups=4, f_keep=2, streams=4),
+    # cached rows of 256 lanes: wider than the attention kernels on the tensor cores take (the plain kernel runs)
+    "w2048_k256": dict(NAGAVIK_SIZES["w2048"], f_heads=16, f_dim=128, f_rot=64, f_vdim=128, q_rank=768, kv_rank=192, r_heads=16,
+                       r_kv_heads=8, r_dim=128, r_vdim=256, f_ff=1024, f_top=4, f_groups=4, f_keep=2, streams=4),
 }
 
 
@@ -722,7 +725,7 @@ def main():
                     help="headline: the 8B numbers only; 14b / 4b: that workload alone (prints its own JSON line); rimopel, "
                          "nagavik: that design at real layer sizes beside Qwen3 at equal size, prefill and decode (its own JSON line); "
                          "fifudra: that design beside Nagavik at equal size, likewise")
-    ap.add_argument("--size", default="", help="rimopel, nagavik, fifudra: one of the workload's sizes only (w2048, w4096)")
+    ap.add_argument("--size", default="", help="rimopel, nagavik, fifudra: one of the workload's sizes only (w2048, w4096; fifudra also w2048_k256)")
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profiling runs)")
     ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill"], help="what to run (profiling runs)")

@@ -35,7 +35,7 @@ def configs():
         # groups and a scale left out, groups of which one is kept; state rows of 64 lanes; a sharp softmax; pages of 16
         "B": (FifudraConfig(vocab=260, width=64, norm_eps=1e-6, streams=4, layers=(
             L("delta", D(heads=2, kv_heads=2, dim=64, vdim=64, conv=4), F("moe", ff=24, experts=8, top=2, scale=2.5, groups=4, keep=2)),
-            L("latent_attention", A(heads=4, dim=16, rot_dim=16, vdim=16, q_rank=24, kv_rank=32, scale=12.0,
+            L("latent_attention", A(heads=4, dim=16, rot_dim=16, vdim=16, q_rank=24, kv_rank=48, scale=12.0,
                                     rot=Rot(base=500.0, dims=16, factor=8.0, original=64.0, fast=8.0, slow=2.0)),
               F("moe", ff=16, experts=6, top=3)),
             L("hgrn2", G(heads=3, dim=16, vdim=8), F("moe", ff=20, experts=4, top=2, scale=0.5, groups=2, keep=1)))), 16),
@@ -48,10 +48,11 @@ def configs():
             L("latent_attention", A(heads=5, dim=6, rot_dim=2, vdim=7, q_rank=5, kv_rank=9, scale=1.0,
                                     rot=Rot(base=50.0, dims=2, factor=1.5, original=16.0, fast=2.0, slow=0.5))),
             L("delta", D(heads=5, kv_heads=1, dim=20, vdim=10, conv=1), F("dense", ff=11)))), 8),
-        # no streams at all (the plain residual sum), no repetition, a convolution of two taps
+        # no streams at all (the plain residual sum), no repetition, a convolution of two taps, three heads on cached rows of
+        # 64 lanes
         "D": (FifudraConfig(vocab=120, width=32, norm_eps=1e-5, embedding_scale=2.0, layers=(
             L("delta", D(heads=2, kv_heads=1, dim=16, vdim=16, conv=2), F("dense", ff=24)),
-            L("latent_attention", A(heads=2, dim=8, rot_dim=8, vdim=8, q_rank=12, kv_rank=16, scale=0.35,
+            L("latent_attention", A(heads=3, dim=8, rot_dim=8, vdim=8, q_rank=12, kv_rank=56, scale=0.35,
                                     rot=Rot(base=10000.0, dims=8)), F("dense", ff=24)),
             L("hgrn2", G(heads=4, dim=8, vdim=8)))), 16),
     }
@@ -266,6 +267,11 @@ def test_what_a_layer_run_keeps_per_request():
     c, _ = configs()["C"]
     specs = models.build_model(c, torch.float32, "cpu").cache_specs()
     assert specs[(2, 1)].shape == (5, 20, 10) and (2, 2) not in specs       # one tap: the convolution keeps nothing
+    # cached rows of 64 lanes in bfloat16: value rows as wide as key rows, for the attention kernels on the tensor cores
+    b, _ = configs()["B"]
+    kv32 = models.build_model(b, torch.float32, "cpu").cache_specs()[(1, 1)]
+    kv16 = models.build_model(b, torch.bfloat16, "cpu").cache_specs()[(1, 1)]
+    assert (kv32.head_dim, kv32.v_head_dim) == (64, 48) and (kv16.head_dim, kv16.v_head_dim) == (64, 0)
 
 
 def test_stretched_frequencies_agree_with_the_plain_ones():
@@ -458,12 +464,13 @@ def test_token_shift_in_portions_equals_the_whole(W, dtype):
 
 @gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("wide", [False, True])
 @pytest.mark.parametrize("q_rank,kv_rank,rot,S,scaling", [(10, 12, 4, 1, True), (5, 9, 2, 2, True), (80, 64, 32, 3, False), (7, 5, 0, 1, False),
                                                           (200, 190, 64, 2, True)])
-def test_latent_norms_rotation_and_store(dtype, q_rank, kv_rank, rot, S, scaling):
+def test_latent_norms_rotation_and_store(dtype, q_rank, kv_rank, rot, S, scaling, wide):
     """From the stacked down projections: both latents normed with their gains, the shared key part rotated by each
     token's position with the stretched frequencies (far positions too), the cache row [c | k_rot] and the value row c
-    in the token's slot; rows without a slot store nothing."""
+    in the token's slot (``wide``: value rows as wide as key rows, zeros behind c); rows without a slot store nothing."""
     from vllm_cpp_b200 import ops
     from vllm_cpp_b200.parts.latent_attention import rope_frequencies
     g = torch.Generator().manual_seed(q_rank + rot)
@@ -475,11 +482,12 @@ def test_latent_norms_rotation_and_store(dtype, q_rank, kv_rank, rot, S, scaling
     slot_map = [9, 10, 11, 0, 17, -1, 3]
     fr, gain = rope_frequencies(rot, 1000.0, sc) if rot else ([0.0], 1.0)
     freq = torch.tensor(fr, dtype=F64).float().to(dev())
-    pages = torch.full((num_pages, ps * (2 * kv_rank + rot)), float("nan"), device=dev(), dtype=dtype)
+    vw = kv_rank + rot if wide else kv_rank
+    pages = torch.full((num_pages, ps * (kv_rank + rot + vw)), float("nan"), device=dev(), dtype=dtype)
     cq = torch.empty(T, q_rank, device=dev(), dtype=dtype)
     status = torch.zeros(1, dtype=torch.int32, device=dev())
     ops.latent_norm_rope_store(partial_sums(u, S, g), f32(gq), f32(gkv), eps, i32(positions), freq, gain, i32(slot_map), cq, pages, ps,
-                               q_rank, kv_rank, rot, status)
+                               q_rank, kv_rank, rot, status, v_width=vw)
     assert status.item() == 0
     tol = TOL32 if dtype == torch.float32 else TOL16
     torch.testing.assert_close(cq.double().cpu(), P.rms_norm(u[:, :q_rank], gq, eps), **tol)
@@ -500,8 +508,9 @@ def test_latent_norms_rotation_and_store(dtype, q_rank, kv_rank, rot, S, scaling
         page, off = slot // ps, slot % ps
         torch.testing.assert_close(host[page, off * khd:off * khd + kv_rank], c[t], **tol)
         torch.testing.assert_close(host[page, off * khd + kv_rank:(off + 1) * khd], k_rot[t], **tol)
-        torch.testing.assert_close(host[page, ps * khd + off * kv_rank:ps * khd + (off + 1) * kv_rank], c[t], **tol)
-    assert (~torch.isnan(host)).sum().item() == 6 * (2 * kv_rank + rot)
+        torch.testing.assert_close(host[page, ps * khd + off * vw:ps * khd + off * vw + kv_rank], c[t], **tol)
+        assert bool((host[page, ps * khd + off * vw + kv_rank:ps * khd + (off + 1) * vw] == 0).all())
+    assert (~torch.isnan(host)).sum().item() == 6 * (kv_rank + rot + vw)
 
 
 @gpu
@@ -719,7 +728,7 @@ def compare(name, dtype, trace, out_dir, requests, oracle):
 
 MODES = {"whole": R.whole, "tail": R.tail_one_by_one, "portions": R.portions, "portions_last": R.portions_last, "mixed": R.mixed,
          "mixed_last": R.mixed_last}
-REPLAYS = ([(n, "float32", m) for n in "ABCD" for m in MODES] + [(n, "bfloat16", m) for n in "ABC" for m in ("whole", "portions", "mixed")])
+REPLAYS = ([(n, "float32", m) for n in "ABCD" for m in MODES] + [(n, "bfloat16", m) for n in "ABCD" for m in ("whole", "portions", "mixed")])
 
 
 @gpu

@@ -48,6 +48,7 @@ struct LatentArgs {
     long long page_stride;
     int page_size, num_pages;
     int q_rank, kv_rank, rot, T;
+    int v_width;            // lanes of a value row: kv_rank, or more (the lanes behind the latent are zeros)
     int* status;
 };
 
@@ -81,12 +82,13 @@ __global__ void latent_norm_rope_store_kernel(LatentArgs a) {
     const int hd = nk + nr;
     TC* base = (TC*)a.pages + (size_t)page * a.page_stride;
     TC* krow = base + (size_t)off * hd;
-    TC* vrow = base + (size_t)a.page_size * hd + (size_t)off * nk;
+    TC* vrow = base + (size_t)a.page_size * hd + (size_t)off * a.v_width;
     for (int c = threadIdx.x; c < nk; c += blockDim.x) {
         const TC v = from_f32<TC>(row[nq + c] * rk * a.gkv[c]);
         krow[c] = v;
         vrow[c] = v;
     }
+    for (int c = nk + threadIdx.x; c < a.v_width; c += blockDim.x) vrow[c] = from_f32<TC>(0.f);
     const int half = nr / 2;
     const float pos = (float)a.positions[t];
     const float* r = row + nq + nk;
@@ -207,15 +209,17 @@ __global__ void rope_rows_kernel(RopeArgs a) {
 }  // namespace
 
 // u [S][T][ld]: q_rank + kv_rank + rot columns.  cq_out [T][q_rank] and the pages in `dtype`.  A page is one flat row:
-// [page_size][kv_rank + rot] key rows, then [page_size][kv_rank] value rows.
+// [page_size][kv_rank + rot] key rows, then [page_size][v_width] value rows (v_width >= kv_rank; the latent, then zeros:
+// value rows as wide as key rows are what the tensor-core attention kernels read).
 VCB_API int vcb_latent_norm_rope_store(const float* u, int S, long long s_stride, long long ld, const float* gq, const float* gkv,
                                        float eps, const int* positions, const float* freq, float gain, const int* slot_map,
                                        void* cq_out, void* pages, long long page_stride, int page_size, int num_pages, int q_rank,
-                                       int kv_rank, int rot, int T, int dtype, int* status, cudaStream_t stream) {
+                                       int kv_rank, int rot, int v_width, int T, int dtype, int* status, cudaStream_t stream) {
     if (T == 0) return 0;
     VCB_CHECK_ARG(q_rank > 0 && kv_rank > 0 && rot >= 0, "latent_norm_rope_store: bad sizes %d %d %d", q_rank, kv_rank, rot);
+    VCB_CHECK_ARG(v_width >= kv_rank && v_width <= kv_rank + rot, "latent_norm_rope_store: value rows of %d lanes", v_width);
     LatentArgs a{Rows{u, S < 1 ? 1 : S, s_stride, ld}, gq, gkv, eps, positions, freq, gain, slot_map, cq_out, pages, page_stride,
-                 page_size, num_pages, q_rank, kv_rank, rot, T, status};
+                 page_size, num_pages, q_rank, kv_rank, rot, T, v_width, status};
     const size_t smem = (size_t)(q_rank + kv_rank + rot) * sizeof(float);
     VCB_CHECK_ARG(smem <= 48 * 1024, "latent_norm_rope_store: %d lanes are more than the kernel's shared memory holds", q_rank + kv_rank + rot);
     if (dtype == VCB_F32) launch_pdl(latent_norm_rope_store_kernel<float>, dim3(T), dim3(256), smem, stream, a);

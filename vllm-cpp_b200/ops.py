@@ -82,7 +82,7 @@ def _declare(L):
         "vcb_moe_route": [P, I, LL, LL, P, P, I, I, I, I, I, P, P, P],
         "vcb_hyper_mix_norm": [P, P, P, I, LL, LL, P, P, P, P, F, P, I, P, I, I, I, I, P],
         "vcb_token_shift": [P, P, P, LL, P, P, P, I, I, I, P, I, P],
-        "vcb_latent_norm_rope_store": [P, I, LL, LL, P, P, F, P, P, F, P, P, P, LL, I, I, I, I, I, I, I, P, P],
+        "vcb_latent_norm_rope_store": [P, I, LL, LL, P, P, F, P, P, F, P, P, P, LL, I, I, I, I, I, I, I, I, P, P],
         "vcb_head_linear": [P, I, I, LL, LL, I, I, P, I, P, I, LL, I, I, I, I, I, I, P],
         "vcb_rope_rows": [P, I, LL, LL, I, I, P, P, F, P, I, LL, I, I, I, I, I, I, P],
         "vcb_matrix_rnn": [I, P, I, LL, LL, P, LL, I, I, I, I, I, P, P, P, P, P, LL, P, P, P, I, I, I, I, I, P, P],
@@ -1073,11 +1073,13 @@ def token_shift(h, mu, state, q_start, q_len, slots, n_entries, out):
 
 
 def latent_norm_rope_store(u, q_gain, kv_gain, eps, positions, freq, gain, slot_map, cq_out, pages, page_size, q_rank,
-                           kv_rank, rot, status):
+                           kv_rank, rot, status, v_width=None):
     """From the stacked down projections ``u`` (32-bit [T, q_rank + kv_rank + rot] or partial sums): the normed query
     latent to ``cq_out`` [T, q_rank]; the normed key/value latent c and the rotated shared key part into the token's
-    cache row.  A page is one flat row: [page_size, kv_rank + rot] key rows [c | k_rot], then [page_size, kv_rank]
-    value rows c.  ``freq`` [rot / 2] 32-bit; cos and sin are multiplied by ``gain``."""
+    cache row.  A page is one flat row: [page_size, kv_rank + rot] key rows [c | k_rot], then [page_size, v_width]
+    value rows [c | zeros] (``v_width`` None: kv_rank lanes, c alone).  ``freq`` [rot / 2] 32-bit; cos and sin are
+    multiplied by ``gain``."""
+    v_width = int(kv_rank if v_width is None else v_width)
     S, ss, ld = _rows_in(u, "u")
     T = u.shape[-2]
     assert u.shape[-1] == q_rank + kv_rank + rot and rot % 2 == 0
@@ -1086,10 +1088,10 @@ def latent_norm_rope_store(u, q_gain, kv_gain, eps, positions, freq, gain, slot_
     if rot:
         _need(freq, "freq", torch.float32); assert freq.numel() == rot // 2
     assert cq_out.shape == (T, q_rank) and q_gain.numel() == q_rank and kv_gain.numel() == kv_rank
-    assert pages[0].numel() == page_size * (2 * kv_rank + rot), (pages.shape, page_size, kv_rank, rot)
+    assert pages[0].numel() == page_size * (kv_rank + rot + v_width), (pages.shape, page_size, kv_rank, rot, v_width)
     _call("vcb_latent_norm_rope_store", _p(u), S, ss, ld, _p(q_gain), _p(kv_gain), float(eps), _p(positions), _p(freq),
           float(gain), _p(slot_map), _p(cq_out), _p(pages), pages.stride(0), int(page_size), pages.shape[0], int(q_rank),
-          int(kv_rank), int(rot), T, _dt(cq_out), _p(status), _stream())
+          int(kv_rank), int(rot), v_width, T, _dt(cq_out), _p(status), _stream())
 
 
 def head_linear(x, m, out, *, heads, n_in, n_out, in_head_stride, in_off=0, out_head_stride, out_off=0):

@@ -15,6 +15,10 @@ Rotation pairs lane i with lane i + r/2; the angle is position * f_i in 32-bit. 
 (``rope_frequencies``): f_i / factor for pairs that turn slowly, f_i for those that turn fast, a linear ramp between,
 and cos and sin times 0.1 ln(factor) + 1.  ``scale`` is used as given.  Norms, angles, scores and softmax are 32-bit;
 the latent rows, the queries and the expanded values are stored in the compute dtype.
+
+Where the attention kernels on the tensor cores take the key rows' width (bfloat16, kv_rank + r of 64 or 128 lanes),
+the value rows are stored as wide as the key rows, [c | zeros]: those kernels read keys and values of one width.  The
+weighted sums then carry r lanes of zeros that the expansion skips; the cache grows by r lanes a token.
 """
 from __future__ import annotations
 
@@ -26,7 +30,7 @@ from .. import ops, workspace
 from ..weights.loader import TensorSpec
 from .base import CacheSpec, Mixer
 from .linear import matmul_tn
-from .window_attention import paged_attention
+from .window_attention import MMA_ATTENTION, paged_attention
 
 
 def rope_frequencies(dims: int, base: float, scaling: dict | None = None):
@@ -73,10 +77,14 @@ class LatentAttention(Mixer):
         freqs, self.rope_gain = rope_frequencies(self.r, float(p.get("rope_base", 10000.0)), p.get("rope_scaling")) \
             if self.r else ([], 1.0)
         self.freq = torch.tensor(freqs or [0.0], dtype=torch.float64).to(torch.float32).to(build.device)
+        # lanes of a cached value row: as many as a key row's where the tensor-core kernels then take both
+        wide = (MMA_ATTENTION and self.r and build.compute_dtype == torch.bfloat16
+                and ops.attn_mma_supported(build.compute_dtype, self.khd))
+        self.vw = self.khd if wide else self.kv_rank
         self.w_down = self.w_uq = self.w_o = self.m_uk = self.m_uv = self.q_gain = self.kv_gain = None
 
     def cache_spec(self):
-        return CacheSpec("kv", num_kv_heads=1, head_dim=self.khd, v_head_dim=self.kv_rank if self.r else 0)
+        return CacheSpec("kv", num_kv_heads=1, head_dim=self.khd, v_head_dim=0 if self.vw == self.khd else self.vw)
 
     def tensor_specs(self):
         p, H, nh = self.prefix, self.hidden, self.nh
@@ -106,15 +114,15 @@ class LatentAttention(Mixer):
         u = matmul_tn(x, self.w_down, ctx.status, out_dtype=torch.float32, allow_partials=True, after_small_kernel=True)
         cq = workspace.empty((T, self.q_rank), dt, dev)
         ops.latent_norm_rope_store(u, self.q_gain, self.kv_gain, self.eps, ctx.positions, self.freq, self.rope_gain,
-                                   group.slot_map, cq, kv.pages, group.page_size, self.q_rank, kr, r, ctx.status)
+                                   group.slot_map, cq, kv.pages, group.page_size, self.q_rank, kr, r, ctx.status, v_width=self.vw)
         q = matmul_tn(cq, self.w_uq, ctx.status, out_dtype=torch.float32, allow_partials=True, after_small_kernel=True)
         ql = workspace.empty((T, nh * khd), dt, dev)
         ops.head_linear(q, self.m_uk, ql, heads=nh, n_in=d, n_out=kr, in_head_stride=d + r, out_head_stride=khd)
         if r:
             ops.rope_rows(q, ctx.positions, self.freq, self.rope_gain, ql, heads=nh, dims=r, width=r, in_head_stride=d + r,
                           in_off=d, out_head_stride=khd, out_off=kr)
-        lat = workspace.empty((T, nh * kr), dt, dev)
-        paged_attention(ctx, kv, ql, lat, nh=nh, nkv=1, hd=khd, vd=kr, scale=self.scale)
+        lat = workspace.empty((T, nh * self.vw), dt, dev)
+        paged_attention(ctx, kv, ql, lat, nh=nh, nkv=1, hd=khd, vd=self.vw, scale=self.scale)
         heads = workspace.empty((T, nh * vd), dt, dev)
-        ops.head_linear(lat, self.m_uv, heads, heads=nh, n_in=kr, n_out=vd, in_head_stride=kr, out_head_stride=vd)
+        ops.head_linear(lat, self.m_uv, heads, heads=nh, n_in=kr, n_out=vd, in_head_stride=self.vw, out_head_stride=vd)
         return matmul_tn(heads, self.w_o, ctx.status, out_dtype=torch.float32, allow_partials=True, after_small_kernel=True)
