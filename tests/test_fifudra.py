@@ -553,6 +553,8 @@ def test_a_small_matrix_per_head_and_the_rotation_of_a_slice(dtype, T, H, n_in, 
 
 PORTION_STEPS = [(3, 1), (1, 1), (2, 7), (1, 2), (9, 1), (1, 0), (2, 2), (1, 1), (1, 1), (1, 1), (16, 1), (1, 17)]
 DECODE_STEPS = [(4, 2)] + [(1, 1)] * 45
+# portions of several staged batches each (the kernels stage 8 or 16 tokens at a time), ending on, before and behind a batch's edge
+LONG_STEPS = [(37, 16), (1, 33), (48, 5), (17, 32), (8, 9), (70, 1)]
 
 
 def run_in_steps(W, steps, S, one_step, seed):
@@ -623,6 +625,12 @@ def test_delta_rule_in_portions_equals_the_whole(H, G, d, dv, taps, S):
 
 
 @gpu
+@pytest.mark.parametrize("H,G,d,dv,taps,S", [(2, 1, 128, 40, 4, 1), (1, 1, 300, 9, 2, 1), (3, 3, 24, 70, 3, 2), (2, 2, 5, 300, 2, 1)])
+def test_delta_rule_in_long_portions(H, G, d, dv, taps, S):
+    check_delta(H, G, d, dv, taps, S, LONG_STEPS)
+
+
+@gpu
 def test_delta_rule_decoding_token_by_token_and_in_bfloat16():
     check_delta(4, 2, 16, 24, 4, 1, DECODE_STEPS)
     check_delta(2, 1, 64, 32, 3, 2, PORTION_STEPS, torch.bfloat16)
@@ -665,6 +673,12 @@ def test_gated_linear_recurrence_in_portions_equals_the_whole(H, d, dv, S):
     """q through a SiLU, the forget gate above its lower bound, what is written is what is not kept; lower bounds up to
     0.995 keep a token for hundreds of steps."""
     check_gated(H, d, dv, S, PORTION_STEPS)
+
+
+@gpu
+@pytest.mark.parametrize("H,d,dv,S", [(2, 128, 48, 1), (1, 270, 11, 1), (3, 20, 66, 2), (2, 3, 280, 1)])
+def test_gated_linear_recurrence_in_long_portions(H, d, dv, S):
+    check_gated(H, d, dv, S, LONG_STEPS)
 
 
 @gpu

@@ -8,17 +8,24 @@
 //  * head_norm_gate          every head of o divided by its root mean square, times a gain shared by the heads, times
 //                            silu(gate) where there is a gate
 //
-// One token after the other is the only order the recurrences allow.  A block owns (entry, head, a tile of value columns):
-// a column's d state rows lie in the registers of L neighbouring lanes (R rows each), whose partial sums meet in shuffles;
-// the inputs of eight tokens are staged in shared memory at a time, so the token loop itself has no barrier.  The order of
-// every sum depends on d only, never on how a prompt was cut: a cut changes nothing but the place of the barrier.
+// One token after the other is the only order the recurrences allow.  A block owns (entry, head, a tile of value columns).
+// Its first WALKERS threads walk the tokens: a column's d state rows lie in the registers of L neighbouring lanes (R rows
+// in a run each, so a token's q and k come as 16-byte words from shared memory), whose partial sums meet in shuffles; a
+// token's read-out is reduced while the next token's first sums are, so one round of shuffles a token is on the critical
+// path.  Its other STAGERS threads meanwhile fetch the next TB tokens' inputs into the other half of a double buffer in
+// shared memory (gates, decays, unit norms done there), so the walk never waits for memory.  A step of decoded tokens runs
+// blocks of WALKERS threads that stage and then walk.  The order of every sum depends on d only, never on how a prompt was
+// cut or on which of the two forms ran: a cut changes nothing but the place of a barrier.
 #include "common.cuh"
 
 namespace {
 
-constexpr int R = 16;          // state rows a thread keeps
-constexpr int TB = 8;          // tokens staged at a time
-constexpr int THREADS = 256;
+constexpr int R = 16;           // state rows a thread keeps: rows kl R .. kl R + R - 1 of its column
+constexpr int PAD = 20;         // lanes a run of R rows takes in shared memory
+constexpr int WALKERS = 256;    // threads that walk the tokens
+constexpr int STAGERS = 256;    // threads that stage the tokens after these
+constexpr int THREADS = WALKERS + STAGERS;
+constexpr int U = 8;            // loads a stager has in flight per kind
 
 struct Rows {
     const float* p;
@@ -32,6 +39,11 @@ __device__ __forceinline__ float rows_at(const Rows& in, long long t, int c) {
     const float* p = in.p + t * in.ld + c;
     for (int s = 0; s < in.S; ++s) v += p[(long long)s * in.s_stride];
     return v;
+}
+
+template <bool ONE>
+__device__ __forceinline__ float sums_at(const Rows& in, long long t, int c) {
+    return ONE ? in.p[t * in.ld + c] : rows_at(in, t, c);
 }
 
 __device__ __forceinline__ int entry_of_row(const int* __restrict__ q_start, const int* __restrict__ q_len, int E, int t) {
@@ -49,6 +61,7 @@ __device__ __forceinline__ int entry_of_row(const int* __restrict__ q_start, con
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ void group_barrier(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
 
 enum { MODE_DELTA = 0, MODE_GATED = 1 };
 
@@ -70,130 +83,257 @@ struct RnnArgs {
     const int* slots;
     float* out;             // [T][H * dv]
     int H, G, d, dv, L;     // G heads of q and k (MODE_DELTA; head h reads h / (H / G))
+    int TB, dp_shift, ct_shift;     // tokens staged at a time; log2(L * R); log2(value columns a block owns)
 };
 
-template <int MODE>
-__global__ __launch_bounds__(THREADS) void matrix_rnn_kernel(RnnArgs a) {
-    extern __shared__ float sm[];
+struct Stage {              // one half of the double buffer
+    float* q;               // [TB][L * PAD]
+    float* k;               // [TB][L * PAD]   (MODE_GATED: the forget gate)
+    float* v;               // [TB][CT]
+    float* g;               // [TB]
+    float* b;               // [TB]
+};
+
+// In shared memory a token's q (or k) rows lie in runs of R with PAD - R unused lanes behind each run, so that the L threads
+// of a column read their R rows as 16-byte words without two of them meeting in a bank.
+__device__ __forceinline__ int padded(int i) { return (i >> 4) * PAD + (i & (R - 1)); }
+
+// the inputs of tokens t_first .. t_first + nb - 1 of (entry, head h, value columns from c0) into `s`; all STAGERS threads.
+// A thread fetches one q/k row (two where a token has more rows than there are stagers) of every tpr-th token, so its
+// addresses differ by a multiple of the row stride only; the loads of a round are all in flight before the first is used.
+// (ONE: the sums are one slice, so a load has no add behind it.)
+template <int MODE, bool ONE>
+__device__ __forceinline__ void stage_tokens(const RnnArgs& a, const Stage& s, int ltid, int h, int hk, long long t_first, int nb,
+                                             int c0) {
+    const int d = a.d, dv = a.dv, DP = 1 << a.dp_shift, DPP = a.L * PAD, CT = 1 << a.ct_shift, TB = a.TB;
+    const int ldx = (int)a.ldx, ldu = (int)a.u.ld;
+    // v, beta and the decay first: their loads fly while q and k are fetched
+    const int vc = ltid & (CT - 1), vt0 = ltid >> a.ct_shift, vstep = STAGERS >> a.ct_shift;    // (vstep == L)
+    const bool v_in = c0 + vc < dv;
+    const float* vp = MODE == MODE_DELTA ? a.x + t_first * a.ldx + a.v_col + h * dv + c0 + vc
+                                         : a.u.p + t_first * a.u.ld + a.v_col + h * dv + c0 + vc;
+    const int ldv = MODE == MODE_DELTA ? ldx : ldu;
+    float vv[2];
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+        const int tt = vt0 + w * vstep;
+        vv[w] = 0.f;
+        if (v_in && tt < nb) vv[w] = (MODE == MODE_DELTA || ONE) ? vp[tt * ldv] : rows_at(a.u, t_first + tt, a.v_col + h * dv + c0 + vc);
+    }
+    float braw = 0.f, araw = 0.f;
+    if (MODE == MODE_DELTA && ltid < nb) {
+        braw = sums_at<ONE>(a.u, t_first + ltid, a.b_col + h);
+        araw = sums_at<ONE>(a.u, t_first + ltid, a.a_col + h);
+    }
+    const int tpr = max(1, STAGERS >> a.dp_shift), tt0 = ltid >> a.dp_shift;
+    for (int i = ltid & (DP - 1); i < DP; i += STAGERS) {
+        const bool in = i < d;
+        const int pi = padded(i);
+        const float *qp, *kp;
+        float low = 0.f, fb = 0.f;
+        if (MODE == MODE_DELTA) {
+            qp = a.x + t_first * a.ldx + a.q_col + hk * d + i;
+            kp = a.x + t_first * a.ldx + a.k_col + hk * d + i;
+        } else {
+            qp = a.u.p + t_first * a.u.ld + a.q_col + h * d + i;
+            kp = a.u.p + t_first * a.u.ld + a.k_col + h * d + i;
+            if (in) {
+                low = a.lower[h * d + i];
+                fb = a.f_bias[h * d + i];
+            }
+        }
+        const int ldq = MODE == MODE_DELTA ? ldx : ldu;
+        for (int tb = tt0; tb < TB; tb += U * tpr) {
+            float qv[U], kv[U];
+#pragma unroll
+            for (int w = 0; w < U; ++w) {
+                const int tt = tb + w * tpr;
+                qv[w] = 0.f;
+                kv[w] = 0.f;
+                if (in && tt < nb) {
+                    if (MODE == MODE_DELTA || ONE) {
+                        qv[w] = qp[tt * ldq];
+                        kv[w] = kp[tt * ldq];
+                    } else {
+                        qv[w] = rows_at(a.u, t_first + tt, a.q_col + h * d + i);
+                        kv[w] = rows_at(a.u, t_first + tt, a.k_col + h * d + i);
+                    }
+                }
+            }
+#pragma unroll
+            for (int w = 0; w < U; ++w) {
+                const int tt = tb + w * tpr;
+                if (tt < TB) {
+                    if (MODE == MODE_GATED && in && tt < nb) {
+                        qv[w] = silu_f(qv[w]);
+                        kv[w] = low + (1.f - low) * sigmoid_f(kv[w] + fb);
+                    }
+                    s.q[tt * DPP + pi] = qv[w];
+                    s.k[tt * DPP + pi] = kv[w];
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+        const int tt = vt0 + w * vstep;
+        if (tt < TB) s.v[tt * CT + vc] = vv[w];
+    }
+    for (int tt = vt0 + 2 * vstep; tt < TB; tt += vstep) {
+        float v = 0.f;
+        if (v_in && tt < nb) v = (MODE == MODE_DELTA || ONE) ? vp[tt * ldv] : rows_at(a.u, t_first + tt, a.v_col + h * dv + c0 + vc);
+        s.v[tt * CT + vc] = v;
+    }
+    if (MODE == MODE_DELTA) {
+        if (ltid < nb) {
+            s.b[ltid] = sigmoid_f(braw);
+            s.g[ltid] = expf(-a.rate[h] * softplus_f(araw + a.dt_bias[h]));
+        }
+        group_barrier(1, STAGERS);
+        // q and k as unit vectors (a warp a token), q times d^(-1/2)
+        const int lane = ltid & 31, warp = ltid >> 5;
+        const float qscale = rsqrtf((float)d);
+        for (int tt = warp; tt < nb; tt += STAGERS / 32) {
+            float* q = s.q + tt * DPP;
+            float* k = s.k + tt * DPP;
+            float sq = 0.f, sk = 0.f;
+            for (int i = lane; i < d; i += 32) {
+                const int pi = padded(i);
+                sq = fmaf(q[pi], q[pi], sq);
+                sk = fmaf(k[pi], k[pi], sk);
+            }
+            sq = warp_sum(sq);
+            sk = warp_sum(sk);
+            const float rq = rsqrtf(sq + 1e-6f) * qscale, rk = rsqrtf(sk + 1e-6f);
+            for (int i = lane; i < d; i += 32) {
+                const int pi = padded(i);
+                q[pi] *= rq;
+                k[pi] *= rk;
+            }
+        }
+    }
+}
+
+// SPLIT: 512 threads, stagers beside walkers (long portions).  Otherwise 256 threads that stage and then walk, several blocks
+// an SM: a step of decoded tokens is many short blocks, which hide one another's waits.
+template <int MODE, bool SPLIT>
+__global__ __launch_bounds__(SPLIT ? THREADS : WALKERS, SPLIT ? 1 : 2) void matrix_rnn_kernel(RnnArgs a) {
+    extern __shared__ __align__(16) float sm[];
     pdl_trigger();
     pdl_wait();
     const int e = blockIdx.z, h = blockIdx.y;
     const int n = a.q_len[e];
     if (n <= 0) return;
-    const int L = a.L, CT = THREADS / L, DP = L * R;
+    const int L = a.L, CT = 1 << a.ct_shift, DPP = L * PAD, TB = a.TB;
     const int d = a.d, dv = a.dv;
-    float* q_s = sm;                    // [TB][DP]
-    float* k_s = q_s + TB * DP;         // [TB][DP]   (MODE_GATED: the forget gate)
-    float* v_s = k_s + TB * DP;         // [TB][CT]
-    float* o_s = v_s + TB * CT;         // [TB][CT]
-    float* g_s = o_s + TB * CT;         // [TB]
-    float* b_s = g_s + TB;              // [TB]
-    const int tid = threadIdx.x, kl = tid % L, col = tid / L;
-    const int j = blockIdx.x * CT + col;
-    const bool live = j < dv;
-    const int lane = tid & 31, warp = tid >> 5;
-    const int t0 = a.q_start[e];
+    const int half = 2 * TB * DPP + TB * CT + 2 * TB;       // (a multiple of four lanes)
+    auto stage_at = [&](int which) {
+        Stage s;
+        s.q = sm + which * half;
+        s.k = s.q + TB * DPP;
+        s.v = s.k + TB * DPP;
+        s.g = s.v + TB * CT;
+        s.b = s.g + TB;
+        return s;
+    };
+    float* o_s = sm + 2 * half;         // [TB][CT]
+    const int tid = threadIdx.x;
+    const bool walker = !SPLIT || tid < WALKERS;
+    const bool stager = !SPLIT || tid >= WALKERS;
+    const int ltid = SPLIT ? tid - WALKERS : tid;
+    const int kl = tid & (L - 1), col = (tid & (WALKERS - 1)) / L;
+    const int c0 = blockIdx.x * CT;
+    const int j = c0 + col;
+    const bool live = walker && j < dv;
+    const long long t0 = a.q_start[e];
+    const int hk = MODE == MODE_DELTA ? h / (a.H / a.G) : h;
+    const bool one = a.u.S == 1;
     float* st = a.state + (size_t)a.slots[e] * a.state_stride + (size_t)h * d * dv;
     float S[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int i = kl + L * r;
+        const int i = kl * R + r;
         S[r] = (live && i < d) ? st[(size_t)i * dv + j] : 0.f;
     }
-    const int hk = MODE == MODE_DELTA ? h / (a.H / a.G) : h;
-    const float qscale = rsqrtf((float)d);
-    for (int b0 = 0; b0 < n; b0 += TB) {
+    const int batches = (n + TB - 1) / TB;
+    if (stager) {
+        if (one) stage_tokens<MODE, true>(a, stage_at(0), ltid, h, hk, t0, min(TB, n), c0);
+        else stage_tokens<MODE, false>(a, stage_at(0), ltid, h, hk, t0, min(TB, n), c0);
+    }
+    __syncthreads();
+    for (int b = 0; b < batches; ++b) {
+        const int b0 = b * TB;
         const int nb = min(TB, n - b0);
-        __syncthreads();      // (everyone is done with the batch before)
-        for (int idx = tid; idx < TB * DP; idx += THREADS) {
-            const int tt = idx / DP, i = idx % DP;
-            float q = 0.f, k = 0.f;
-            if (tt < nb && i < d) {
-                const long long t = t0 + b0 + tt;
+        if (walker) {
+            const Stage s = stage_at(b & 1);
+            const float4* q4 = reinterpret_cast<const float4*>(s.q + kl * PAD);
+            const float4* k4 = reinterpret_cast<const float4*>(s.k + kl * PAD);
+            const int step4 = DPP / 4;
+            float o_prev = 0.f;
+            for (int tt = 0; tt < nb; ++tt) {
+                float kr[R], qr[R];
+#pragma unroll
+                for (int r = 0; r < R / 4; ++r) {
+                    const float4 kk = k4[tt * step4 + r];
+                    kr[4 * r] = kk.x; kr[4 * r + 1] = kk.y; kr[4 * r + 2] = kk.z; kr[4 * r + 3] = kk.w;
+                }
+#pragma unroll
+                for (int r = 0; r < R / 4; ++r) {
+                    const float4 qq = q4[tt * step4 + r];
+                    qr[4 * r] = qq.x; qr[4 * r + 1] = qq.y; qr[4 * r + 2] = qq.z; qr[4 * r + 3] = qq.w;
+                }
+                const float v = s.v[tt * CT + col];
+                float o4[4] = {0.f, 0.f, 0.f, 0.f};
                 if (MODE == MODE_DELTA) {
-                    q = a.x[t * a.ldx + a.q_col + hk * d + i];
-                    k = a.x[t * a.ldx + a.k_col + hk * d + i];
+                    const float g = s.g[tt], beta = s.b[tt];
+                    float p4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int r = 0; r < R; ++r) p4[r & 3] = fmaf(S[r], kr[r], p4[r & 3]);
+                    float p = (p4[0] + p4[1]) + (p4[2] + p4[3]);
+                    // the read-out of the token before is reduced beside this token's S^T k
+                    for (int off = 1; off < L; off <<= 1) {
+                        p += __shfl_xor_sync(0xffffffffu, p, off);
+                        o_prev += __shfl_xor_sync(0xffffffffu, o_prev, off);
+                    }
+                    if (tt > 0 && kl == 0) o_s[(tt - 1) * CT + col] = o_prev;
+                    const float w = beta * (v - g * p);
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        S[r] = fmaf(kr[r], w, g * S[r]);
+                        o4[r & 3] = fmaf(S[r], qr[r], o4[r & 3]);
+                    }
                 } else {
-                    const int c = h * d + i;
-                    q = silu_f(rows_at(a.u, t, a.q_col + c));
-                    const float low = a.lower[c];
-                    k = low + (1.f - low) * sigmoid_f(rows_at(a.u, t, a.k_col + c) + a.f_bias[c]);
-                }
-            }
-            q_s[idx] = q;
-            k_s[idx] = k;
-        }
-        for (int idx = tid; idx < TB * CT; idx += THREADS) {
-            const int tt = idx / CT, c = blockIdx.x * CT + idx % CT;
-            float v = 0.f;
-            if (tt < nb && c < dv) {
-                const long long t = t0 + b0 + tt;
-                v = MODE == MODE_DELTA ? a.x[t * a.ldx + a.v_col + h * dv + c] : rows_at(a.u, t, a.v_col + h * dv + c);
-            }
-            v_s[idx] = v;
-        }
-        if (MODE == MODE_DELTA && tid < nb) {
-            const long long t = t0 + b0 + tid;
-            b_s[tid] = sigmoid_f(rows_at(a.u, t, a.b_col + h));
-            g_s[tid] = expf(-a.rate[h] * softplus_f(rows_at(a.u, t, a.a_col + h) + a.dt_bias[h]));
-        }
-        __syncthreads();
-        if (MODE == MODE_DELTA) {
-            // q and k as unit vectors (a warp a token)
-            for (int tt = warp; tt < nb; tt += THREADS / 32) {
-                float sq = 0.f, sk = 0.f;
-                for (int i = lane; i < d; i += 32) {
-                    sq = fmaf(q_s[tt * DP + i], q_s[tt * DP + i], sq);
-                    sk = fmaf(k_s[tt * DP + i], k_s[tt * DP + i], sk);
-                }
-                sq = warp_sum(sq);
-                sk = warp_sum(sk);
-                const float rq = rsqrtf(sq + 1e-6f) * qscale, rk = rsqrtf(sk + 1e-6f);
-                for (int i = lane; i < d; i += 32) {
-                    q_s[tt * DP + i] *= rq;
-                    k_s[tt * DP + i] *= rk;
-                }
-            }
-            __syncthreads();
-        }
-        for (int tt = 0; tt < nb; ++tt) {
-            const float* qq = q_s + tt * DP + kl;
-            const float* kk = k_s + tt * DP + kl;
-            const float v = v_s[tt * CT + col];
-            float o = 0.f;
-            if (MODE == MODE_DELTA) {
-                float p = 0.f;
 #pragma unroll
-                for (int r = 0; r < R; ++r) p = fmaf(S[r], kk[L * r], p);
-                for (int off = 1; off < L; off <<= 1) p += __shfl_xor_sync(0xffffffffu, p, off);
-                const float g = g_s[tt];
-                const float w = b_s[tt] * (v - g * p);
-#pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    S[r] = fmaf(kk[L * r], w, g * S[r]);
-                    o = fmaf(S[r], qq[L * r], o);
+                    for (int r = 0; r < R; ++r) {
+                        const float f = kr[r];
+                        S[r] = fmaf(f, S[r], (1.f - f) * v);
+                        o4[r & 3] = fmaf(S[r], qr[r], o4[r & 3]);
+                    }
+                    for (int off = 1; off < L; off <<= 1) o_prev += __shfl_xor_sync(0xffffffffu, o_prev, off);
+                    if (tt > 0 && kl == 0) o_s[(tt - 1) * CT + col] = o_prev;
                 }
-            } else {
-#pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const float f = kk[L * r];
-                    S[r] = fmaf(f, S[r], (1.f - f) * v);
-                    o = fmaf(S[r], qq[L * r], o);
-                }
+                o_prev = (o4[0] + o4[1]) + (o4[2] + o4[3]);
             }
-            for (int off = 1; off < L; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-            if (kl == 0) o_s[tt * CT + col] = o;
+            for (int off = 1; off < L; off <<= 1) o_prev += __shfl_xor_sync(0xffffffffu, o_prev, off);
+            if (kl == 0) o_s[(nb - 1) * CT + col] = o_prev;
+            group_barrier(2, WALKERS);
+            float* orow = a.out + (size_t)(t0 + b0) * (a.H * dv) + h * dv + c0;
+            for (int idx = tid; idx < nb * CT; idx += WALKERS) {
+                const int tt = idx >> a.ct_shift, c = idx & (CT - 1);
+                if (c0 + c < dv) orow[(size_t)tt * (a.H * dv) + c] = o_s[idx];
+            }
         }
-        __syncthreads();
-        for (int idx = tid; idx < nb * CT; idx += THREADS) {
-            const int tt = idx / CT, c = blockIdx.x * CT + idx % CT;
-            if (c < dv) a.out[(size_t)(t0 + b0 + tt) * (a.H * dv) + h * dv + c] = o_s[tt * CT + idx % CT];
+        if (stager && b + 1 < batches) {
+            const int nn = min(TB, n - b0 - TB);
+            if (one) stage_tokens<MODE, true>(a, stage_at((b + 1) & 1), ltid, h, hk, t0 + b0 + TB, nn, c0);
+            else stage_tokens<MODE, false>(a, stage_at((b + 1) & 1), ltid, h, hk, t0 + b0 + TB, nn, c0);
         }
+        __syncthreads();      // the walkers are done with this half and with o_s, the stagers have filled the other half
     }
     if (live) {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
-            const int i = kl + L * r;
+            const int i = kl * R + r;
             if (i < d) st[(size_t)i * dv + j] = S[r];
         }
     }
@@ -235,24 +375,35 @@ int rnn_lanes(int d) {
 }  // namespace
 
 // mode 0: the gated delta rule; 1: the gated linear form (see the head of this file).  u [S][T][ld] the projection's sums;
-// x [T][ldx] the convolved rows (mode 0).  state [slots][H][d][dv].  out [T][H * dv] 32-bit.  Entries of no tokens are left out.
+// x [T][ldx] the convolved rows (mode 0).  state [slots][H][d][dv].  out [rows][H * dv] 32-bit, rows >= the entries' tokens.  Entries of no tokens are left out.
 VCB_API int vcb_matrix_rnn(int mode, const float* u, int S, long long s_stride, long long ld, const float* x, long long ldx,
                            int q_col, int k_col, int v_col, int b_col, int a_col, const float* dt_bias, const float* rate,
                            const float* f_bias, const float* lower, float* state, long long state_stride, const int* q_start,
-                           const int* q_len, const int* slots, int E, int H, int G, int d, int dv, float* out,
+                           const int* q_len, const int* slots, int E, int rows, int H, int G, int d, int dv, float* out,
                            cudaStream_t stream) {
     if (E == 0) return 0;
     VCB_CHECK_ARG(mode == 0 || mode == 1, "matrix_rnn: unknown mode %d", mode);
     VCB_CHECK_ARG(d >= 1 && d <= 32 * R, "matrix_rnn: %d state rows a head (1 to %d)", d, 32 * R);
     VCB_CHECK_ARG(H >= 1 && G >= 1 && H % G == 0 && dv >= 1, "matrix_rnn: bad sizes H=%d G=%d dv=%d", H, G, dv);
     VCB_CHECK_ARG(H <= 65535 && E <= 65535, "matrix_rnn: %d heads, %d entries", H, E);
-    const int L = rnn_lanes(d), CT = THREADS / L, DP = L * R;
+    const int L = rnn_lanes(d), CT = WALKERS / L, DP = L * R;
+    const int TB = DP <= 256 ? 16 : 8;
+    int dp_shift = 0, ct_shift = 0;
+    while ((1 << dp_shift) < DP) ++dp_shift;
+    while ((1 << ct_shift) < CT) ++ct_shift;
+    VCB_CHECK_ARG(ld < (1 << 26) && ldx < (1 << 26), "matrix_rnn: rows of %lld and %lld lanes", ld, ldx);
     RnnArgs a{Rows{u, S < 1 ? 1 : S, s_stride, ld}, x, ldx, q_col, k_col, v_col, b_col, a_col, dt_bias, rate, f_bias, lower, state,
-              state_stride, q_start, q_len, slots, out, H, G, d, dv, L};
-    const size_t smem = (size_t)(2 * TB * DP + 2 * TB * CT + 2 * TB) * sizeof(float);
+              state_stride, q_start, q_len, slots, out, H, G, d, dv, L, TB, dp_shift, ct_shift};
+    const size_t smem = (size_t)(2 * (2 * TB * L * PAD + TB * CT + 2 * TB) + TB * CT) * sizeof(float);
     const dim3 grid((dv + CT - 1) / CT, H, E);
-    if (mode == 0) launch_pdl(matrix_rnn_kernel<MODE_DELTA>, grid, dim3(THREADS), smem, stream, a);
-    else launch_pdl(matrix_rnn_kernel<MODE_GATED>, grid, dim3(THREADS), smem, stream, a);
+    const bool split = rows > 4 * E;    // some entry has more than four tokens
+    auto kern = split ? (mode == 0 ? matrix_rnn_kernel<MODE_DELTA, true> : matrix_rnn_kernel<MODE_GATED, true>)
+                      : (mode == 0 ? matrix_rnn_kernel<MODE_DELTA, false> : matrix_rnn_kernel<MODE_GATED, false>);
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        vcb_set_error("matrix_rnn: %zu bytes of shared memory refused", smem);
+        return -2;
+    }
+    launch_pdl(kern, grid, dim3(split ? THREADS : WALKERS), smem, stream, a);
     VCB_CHECK_LAUNCH("matrix_rnn");
     return 0;
 }

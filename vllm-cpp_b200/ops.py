@@ -85,7 +85,7 @@ def _declare(L):
         "vcb_latent_norm_rope_store": [P, I, LL, LL, P, P, F, P, P, F, P, P, P, LL, I, I, I, I, I, I, I, I, P, P],
         "vcb_head_linear": [P, I, I, LL, LL, I, I, P, I, P, I, LL, I, I, I, I, I, I, P],
         "vcb_rope_rows": [P, I, LL, LL, I, I, P, P, F, P, I, LL, I, I, I, I, I, I, P],
-        "vcb_matrix_rnn": [I, P, I, LL, LL, P, LL, I, I, I, I, I, P, P, P, P, P, LL, P, P, P, I, I, I, I, I, P, P],
+        "vcb_matrix_rnn": [I, P, I, LL, LL, P, LL, I, I, I, I, I, P, P, P, P, P, LL, P, P, P, I, I, I, I, I, I, P, P],
         "vcb_head_norm_gate": [P, P, I, LL, LL, I, P, F, P, P, I, I, I, I, P, I, P],
         "vcb_moe_route_grouped": [P, I, LL, LL, P, I, I, F, P, P, I, I, I, I, P, P, P],
         "vcb_moe_group": [P, I, I, I, I, P, P, P, P],
@@ -1154,7 +1154,7 @@ def matrix_rnn(mode, u, state, q_start, q_len, slots, n_entries, out, *, heads, 
             _need(t, name, torch.float32); assert t.numel() == heads * d
     _call("vcb_matrix_rnn", m, _p(u), S, ss, ld, _p(x), ldx, int(q_col), int(k_col), int(v_col), int(b_col), int(a_col),
           _p(dt_bias), _p(rate), _p(f_bias), _p(lower), _p(state), state.stride(0), _p(q_start), _p(q_len), _p(slots),
-          n_entries, int(heads), int(kv_heads or heads), int(d), int(dv), _p(out), _stream())
+          n_entries, int(out.shape[0]), int(heads), int(kv_heads or heads), int(d), int(dv), _p(out), _stream())
 
 
 def head_norm_gate(o, weight, eps, q_start, q_len, n_entries, heads, dv, out, gate=None, gate_col=0):
