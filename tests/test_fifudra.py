@@ -259,14 +259,14 @@ def test_what_a_layer_run_keeps_per_request():
     kv = specs[(0, 1)]
     assert (kv.kind, kv.num_kv_heads, kv.head_dim, kv.v_head_dim) == ("kv", 1, 12 + 4, 12)       # the latent and the rotated key part
     for run in (1, 3):
-        assert (specs[(run, 1)].shape, specs[(run, 1)].dtype) == ((4, 8, 12), "float32")
+        assert (specs[(run, 1)].shape, specs[(run, 1)].dtype) == ((4, 12, 8), "float32")          # heads, value columns, rows
         assert specs[(run, 2)].shape == (2, 2 * 16 + 48)                                       # the convolution's last inputs
     for run in (2, 4):
-        assert specs[(run, 1)].shape == (2, 6, 10)
+        assert specs[(run, 1)].shape == (2, 10, 6)
     assert (specs[(5, 1)].head_dim, specs[(5, 1)].v_head_dim) == (5 + 8, 5)
     c, _ = configs()["C"]
     specs = models.build_model(c, torch.float32, "cpu").cache_specs()
-    assert specs[(2, 1)].shape == (5, 20, 10) and (2, 2) not in specs       # one tap: the convolution keeps nothing
+    assert specs[(2, 1)].shape == (5, 10, 20) and (2, 2) not in specs       # one tap: the convolution keeps nothing
     # cached rows of 64 lanes in bfloat16: value rows as wide as key rows, for the attention kernels on the tensor cores
     b, _ = configs()["B"]
     kv32 = models.build_model(b, torch.float32, "cpu").cache_specs()[(1, 1)]
@@ -586,7 +586,7 @@ def check_delta(H, G, d, dv, taps, S, steps, dtype=torch.float32):
          "A_log": torch.linspace(-6.0, 0.5, H, dtype=F64), "dt_bias": rnd(H), "norm": 1 + 0.2 * rnd(dv), "o": torch.eye(inner, dtype=F64)}
     w_in = torch.cat([w[n] for n in ("q", "k", "v", "g", "b", "a")])
     conv_w = f32(torch.cat([w["q.conv"], w["k.conv"], w["v.conv"]]))
-    state = torch.zeros(3, H, d, dv, device=dev())
+    state = torch.zeros(3, H, dv, d, device=dev())
     state[1] = float("nan")
     conv_state = torch.zeros(3, taps - 1, cc, device=dev()) if taps > 1 else None
     rate, dt_bias, gain = f32(torch.exp(w["A_log"])), f32(w["dt_bias"]), f32(w["norm"])
@@ -645,7 +645,7 @@ def check_gated(H, d, dv, S, steps, dtype=torch.float32):
     w = {"q": rnd(qk, W), "f": rnd(qk, W), "f.b": rnd(qk), "lower": torch.linspace(0.0, 0.995, qk, dtype=F64), "v": rnd(inner, W),
          "norm": 1 + 0.2 * rnd(dv), "o": torch.eye(inner, dtype=F64)}
     w_in = torch.cat([w["q"], w["f"], w["v"]])
-    state = torch.zeros(3, H, d, dv, device=dev())
+    state = torch.zeros(3, H, dv, d, device=dev())
     state[1] = float("nan")
     f_bias, lower, gain = f32(w["f.b"]), f32(w["lower"]), f32(w["norm"])
 

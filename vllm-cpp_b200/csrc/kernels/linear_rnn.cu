@@ -9,19 +9,19 @@
 //                            silu(gate) where there is a gate
 //
 // One token after the other is the only order the recurrences allow.  A block owns (entry, head, a tile of value columns).
-// Its first WALKERS threads walk the tokens: a column's d state rows lie in the registers of L neighbouring lanes (R rows
-// in a run each, so a token's q and k come as 16-byte words from shared memory), whose partial sums meet in shuffles; a
-// token's read-out is reduced while the next token's first sums are, so one round of shuffles a token is on the critical
-// path.  Its other STAGERS threads meanwhile fetch the next TB tokens' inputs into the other half of a double buffer in
-// shared memory (gates, decays, unit norms done there), so the walk never waits for memory.  A step of decoded tokens runs
-// blocks of WALKERS threads that stage and then walk.  The order of every sum depends on d only, never on how a prompt was
-// cut or on which of the two forms ran: a cut changes nothing but the place of a barrier.
+// Its first WALKERS threads walk the tokens: a thread keeps R rows of two neighbouring columns in registers, in pieces of
+// four rows dealt round to the L neighbouring lanes that share the columns, so a token's q and k come as 16-byte words
+// from shared memory (each serving both columns) and the state as 16-byte words from its slot; the arithmetic runs on
+// pairs of 32-bit lanes (fma.rn.f32x2).  The lanes' partial sums meet in shuffles; a token's read-out is reduced in the
+// same rounds as the next token's S^T k, so one set of rounds a token is on the critical path.  Its other STAGERS threads
+// meanwhile fetch the next TB tokens' inputs into the other half of a double buffer in shared memory (gates, decays,
+// unit norms done there), so the walk never waits for memory.  A step of decoded tokens runs blocks of WALKERS threads
+// that stage and then walk.  The order of every sum depends on d only, never on how a prompt was cut or on which of the
+// two forms ran: a cut changes nothing but the place of a barrier.
 #include "common.cuh"
 
 namespace {
 
-constexpr int R = 16;           // state rows a thread keeps: rows kl R .. kl R + R - 1 of its column
-constexpr int PAD = 20;         // lanes a run of R rows takes in shared memory
 constexpr int WALKERS = 256;    // threads that walk the tokens
 constexpr int STAGERS = 256;    // threads that stage the tokens after these
 constexpr int THREADS = WALKERS + STAGERS;
@@ -61,6 +61,25 @@ __device__ __forceinline__ int entry_of_row(const int* __restrict__ q_start, con
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+// two 32-bit lanes in one 64-bit register; fma.rn.f32x2 and mul.rn.f32x2 are an IEEE operation on each lane
+__device__ __forceinline__ uint64_t pair_f32(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpair_f32(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_pair(uint64_t x, uint64_t y, uint64_t z) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(x), "l"(y), "l"(z));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul_pair(uint64_t x, uint64_t y) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(x), "l"(y));
+    return d;
+}
 __device__ __forceinline__ void group_barrier(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
 
 enum { MODE_DELTA = 0, MODE_GATED = 1 };
@@ -76,7 +95,7 @@ struct RnnArgs {
     const float* rate;      // [H] exp(A_log)
     const float* f_bias;    // MODE_GATED: [H * d]
     const float* lower;     // MODE_GATED: [H * d]
-    float* state;           // [slots][H][d][dv]
+    float* state;           // [slots][H][dv][d]
     long long state_stride;
     const int* q_start;
     const int* q_len;
@@ -87,39 +106,33 @@ struct RnnArgs {
 };
 
 struct Stage {              // one half of the double buffer
-    float* q;               // [TB][L * PAD]
-    float* k;               // [TB][L * PAD]   (MODE_GATED: the forget gate)
+    float* q;               // [TB][L * R]
+    float* k;               // [TB][L * R]   (MODE_GATED: the forget gate)
     float* v;               // [TB][CT]
     float* g;               // [TB]
     float* b;               // [TB]
 };
 
-// In shared memory a token's q (or k) rows lie in runs of R with PAD - R unused lanes behind each run, so that the L threads
-// of a column read their R rows as 16-byte words without two of them meeting in a bank.
-__device__ __forceinline__ int padded(int i) { return (i >> 4) * PAD + (i & (R - 1)); }
-
 // the inputs of tokens t_first .. t_first + nb - 1 of (entry, head h, value columns from c0) into `s`; all STAGERS threads.
 // A thread fetches one q/k row (two where a token has more rows than there are stagers) of every tpr-th token, so its
 // addresses differ by a multiple of the row stride only; the loads of a round are all in flight before the first is used.
 // (ONE: the sums are one slice, so a load has no add behind it.)
-template <int MODE, bool ONE>
+template <int MODE, bool ONE, int R>
 __device__ __forceinline__ void stage_tokens(const RnnArgs& a, const Stage& s, int ltid, int h, int hk, long long t_first, int nb,
                                              int c0) {
-    const int d = a.d, dv = a.dv, DP = 1 << a.dp_shift, DPP = a.L * PAD, CT = 1 << a.ct_shift, TB = a.TB;
+    const int d = a.d, dv = a.dv, DP = 1 << a.dp_shift, DPP = DP, CT = 1 << a.ct_shift, TB = a.TB;
     const int ldx = (int)a.ldx, ldu = (int)a.u.ld;
     // v, beta and the decay first: their loads fly while q and k are fetched
-    const int vc = ltid & (CT - 1), vt0 = ltid >> a.ct_shift, vstep = STAGERS >> a.ct_shift;    // (vstep == L)
-    const bool v_in = c0 + vc < dv;
-    const float* vp = MODE == MODE_DELTA ? a.x + t_first * a.ldx + a.v_col + h * dv + c0 + vc
-                                         : a.u.p + t_first * a.u.ld + a.v_col + h * dv + c0 + vc;
+    const float* vp = MODE == MODE_DELTA ? a.x + t_first * a.ldx + a.v_col + h * dv + c0 : a.u.p + t_first * a.u.ld + a.v_col + h * dv + c0;
     const int ldv = MODE == MODE_DELTA ? ldx : ldu;
+    auto v_at = [&](int idx) {
+        const int tt = idx >> a.ct_shift, c = idx & (CT - 1);
+        if (idx >= TB * CT || tt >= nb || c0 + c >= dv) return 0.f;
+        return (MODE == MODE_DELTA || ONE) ? vp[tt * ldv + c] : rows_at(a.u, t_first + tt, a.v_col + h * dv + c0 + c);
+    };
     float vv[2];
 #pragma unroll
-    for (int w = 0; w < 2; ++w) {
-        const int tt = vt0 + w * vstep;
-        vv[w] = 0.f;
-        if (v_in && tt < nb) vv[w] = (MODE == MODE_DELTA || ONE) ? vp[tt * ldv] : rows_at(a.u, t_first + tt, a.v_col + h * dv + c0 + vc);
-    }
+    for (int w = 0; w < 2; ++w) vv[w] = v_at(ltid + w * STAGERS);
     float braw = 0.f, araw = 0.f;
     if (MODE == MODE_DELTA && ltid < nb) {
         braw = sums_at<ONE>(a.u, t_first + ltid, a.b_col + h);
@@ -128,7 +141,7 @@ __device__ __forceinline__ void stage_tokens(const RnnArgs& a, const Stage& s, i
     const int tpr = max(1, STAGERS >> a.dp_shift), tt0 = ltid >> a.dp_shift;
     for (int i = ltid & (DP - 1); i < DP; i += STAGERS) {
         const bool in = i < d;
-        const int pi = padded(i);
+        const int pi = i;
         const float *qp, *kp;
         float low = 0.f, fb = 0.f;
         if (MODE == MODE_DELTA) {
@@ -175,15 +188,9 @@ __device__ __forceinline__ void stage_tokens(const RnnArgs& a, const Stage& s, i
         }
     }
 #pragma unroll
-    for (int w = 0; w < 2; ++w) {
-        const int tt = vt0 + w * vstep;
-        if (tt < TB) s.v[tt * CT + vc] = vv[w];
-    }
-    for (int tt = vt0 + 2 * vstep; tt < TB; tt += vstep) {
-        float v = 0.f;
-        if (v_in && tt < nb) v = (MODE == MODE_DELTA || ONE) ? vp[tt * ldv] : rows_at(a.u, t_first + tt, a.v_col + h * dv + c0 + vc);
-        s.v[tt * CT + vc] = v;
-    }
+    for (int w = 0; w < 2; ++w)
+        if (ltid + w * STAGERS < TB * CT) s.v[ltid + w * STAGERS] = vv[w];
+    for (int idx = ltid + 2 * STAGERS; idx < TB * CT; idx += STAGERS) s.v[idx] = v_at(idx);
     if (MODE == MODE_DELTA) {
         if (ltid < nb) {
             s.b[ltid] = sigmoid_f(braw);
@@ -198,7 +205,7 @@ __device__ __forceinline__ void stage_tokens(const RnnArgs& a, const Stage& s, i
             float* k = s.k + tt * DPP;
             float sq = 0.f, sk = 0.f;
             for (int i = lane; i < d; i += 32) {
-                const int pi = padded(i);
+                const int pi = i;
                 sq = fmaf(q[pi], q[pi], sq);
                 sk = fmaf(k[pi], k[pi], sk);
             }
@@ -206,7 +213,7 @@ __device__ __forceinline__ void stage_tokens(const RnnArgs& a, const Stage& s, i
             sk = warp_sum(sk);
             const float rq = rsqrtf(sq + 1e-6f) * qscale, rk = rsqrtf(sk + 1e-6f);
             for (int i = lane; i < d; i += 32) {
-                const int pi = padded(i);
+                const int pi = i;
                 q[pi] *= rq;
                 k[pi] *= rk;
             }
@@ -215,8 +222,10 @@ __device__ __forceinline__ void stage_tokens(const RnnArgs& a, const Stage& s, i
 }
 
 // SPLIT: 512 threads, stagers beside walkers (long portions).  Otherwise 256 threads that stage and then walk, several blocks
-// an SM: a step of decoded tokens is many short blocks, which hide one another's waits.
-template <int MODE, bool SPLIT>
+// an SM: a step of decoded tokens is many short blocks, which hide one another's waits.  R: state rows a thread keeps of
+// each of its C (one or two) columns: one column a thread where that still fills the GPU's SMs once, else two, which
+// halves the shared-memory reads a column.
+template <int MODE, bool SPLIT, int R, int C>
 __global__ __launch_bounds__(SPLIT ? THREADS : WALKERS, SPLIT ? 1 : 2) void matrix_rnn_kernel(RnnArgs a) {
     extern __shared__ __align__(16) float sm[];
     pdl_trigger();
@@ -224,7 +233,7 @@ __global__ __launch_bounds__(SPLIT ? THREADS : WALKERS, SPLIT ? 1 : 2) void matr
     const int e = blockIdx.z, h = blockIdx.y;
     const int n = a.q_len[e];
     if (n <= 0) return;
-    const int L = a.L, CT = 1 << a.ct_shift, DPP = L * PAD, TB = a.TB;
+    const int L = a.L, CT = 1 << a.ct_shift, DPP = L * R, TB = a.TB;
     const int d = a.d, dv = a.dv;
     const int half = 2 * TB * DPP + TB * CT + 2 * TB;       // (a multiple of four lanes)
     auto stage_at = [&](int which) {
@@ -241,24 +250,42 @@ __global__ __launch_bounds__(SPLIT ? THREADS : WALKERS, SPLIT ? 1 : 2) void matr
     const bool walker = !SPLIT || tid < WALKERS;
     const bool stager = !SPLIT || tid >= WALKERS;
     const int ltid = SPLIT ? tid - WALKERS : tid;
-    const int kl = tid & (L - 1), col = (tid & (WALKERS - 1)) / L;
+    const int kl = tid & (L - 1), cg = (tid & (WALKERS - 1)) / L;       // this thread's columns: c0 + C cg, and the next
     const int c0 = blockIdx.x * CT;
-    const int j = c0 + col;
-    const bool live = walker && j < dv;
     const long long t0 = a.q_start[e];
     const int hk = MODE == MODE_DELTA ? h / (a.H / a.G) : h;
     const bool one = a.u.S == 1;
-    float* st = a.state + (size_t)a.slots[e] * a.state_stride + (size_t)h * d * dv;
-    float S[R];
+    float* st = a.state + (size_t)a.slots[e] * a.state_stride + (size_t)h * d * dv;     // [dv][d]: a column's rows in a run
+    // this thread's rows: the pieces of four 4 (kl + L m) .. + 3, m < R / 4, so that the L threads of a column read
+    // neighbouring 16-byte words of q, k and the state.  Pairs of rows in a 64-bit register: the multiply-adds run on pairs.
+    uint64_t S[C][R / 2];
+    const bool vec = (d & 3) == 0 && (reinterpret_cast<uintptr_t>(st) & 15) == 0;
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int i = kl * R + r;
-        S[r] = (live && i < d) ? st[(size_t)i * dv + j] : 0.f;
+    for (int c = 0; c < C; ++c) {
+        const int j = c0 + cg * C + c;
+        const bool in = walker && j < dv;
+#pragma unroll
+        for (int m = 0; m < R / 4; ++m) {
+            const int i = 4 * (kl + L * m);
+            float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (in && i < d) {
+                const float* src = st + (size_t)j * d + i;
+                if (vec) t = *reinterpret_cast<const float4*>(src);
+                else {
+                    t.x = src[0];
+                    if (i + 1 < d) t.y = src[1];
+                    if (i + 2 < d) t.z = src[2];
+                    if (i + 3 < d) t.w = src[3];
+                }
+            }
+            S[c][2 * m] = pair_f32(t.x, t.y);
+            S[c][2 * m + 1] = pair_f32(t.z, t.w);
+        }
     }
     const int batches = (n + TB - 1) / TB;
     if (stager) {
-        if (one) stage_tokens<MODE, true>(a, stage_at(0), ltid, h, hk, t0, min(TB, n), c0);
-        else stage_tokens<MODE, false>(a, stage_at(0), ltid, h, hk, t0, min(TB, n), c0);
+        if (one) stage_tokens<MODE, true, R>(a, stage_at(0), ltid, h, hk, t0, min(TB, n), c0);
+        else stage_tokens<MODE, false, R>(a, stage_at(0), ltid, h, hk, t0, min(TB, n), c0);
     }
     __syncthreads();
     for (int b = 0; b < batches; ++b) {
@@ -266,56 +293,118 @@ __global__ __launch_bounds__(SPLIT ? THREADS : WALKERS, SPLIT ? 1 : 2) void matr
         const int nb = min(TB, n - b0);
         if (walker) {
             const Stage s = stage_at(b & 1);
-            const float4* q4 = reinterpret_cast<const float4*>(s.q + kl * PAD);
-            const float4* k4 = reinterpret_cast<const float4*>(s.k + kl * PAD);
+            const ulonglong2* q4 = reinterpret_cast<const ulonglong2*>(s.q) + kl;
+            const ulonglong2* k4 = reinterpret_cast<const ulonglong2*>(s.k) + kl;
+            const float* vcol = s.v + cg * C;
             const int step4 = DPP / 4;
-            float o_prev = 0.f;
+            const bool odd = kl & 1;
+            float o_prev[C];
+#pragma unroll
+            for (int c = 0; c < C; ++c) o_prev[c] = 0.f;
+            // The read-out of one token is reduced in the same rounds as the next token's S^T k (`with_p`).  With two
+            // columns the lanes first swap a column of the read-out each, then add up the one they kept: lanes 0 and 1 of
+            // the L end with the sums of the first and the second column.  p is summed to every lane.
+            auto reduce = [&](int tt_of, bool with_p, float* p) {
+                if (L > 1) {
+                    float keep;
+                    if (C == 2) keep = (odd ? o_prev[C - 1] : o_prev[0]) + __shfl_xor_sync(0xffffffffu, odd ? o_prev[0] : o_prev[C - 1], 1);
+                    else keep = o_prev[0] + __shfl_xor_sync(0xffffffffu, o_prev[0], 1);
+                    if (with_p) {
+#pragma unroll
+                        for (int c = 0; c < C; ++c) p[c] += __shfl_xor_sync(0xffffffffu, p[c], 1);
+                    }
+                    for (int off = 2; off < L; off <<= 1) {
+                        keep += __shfl_xor_sync(0xffffffffu, keep, off);
+                        if (with_p) {
+#pragma unroll
+                            for (int c = 0; c < C; ++c) p[c] += __shfl_xor_sync(0xffffffffu, p[c], off);
+                        }
+                    }
+                    if (tt_of >= 0 && kl < C) o_s[tt_of * CT + cg * C + kl] = keep;
+                } else if (tt_of >= 0) {
+#pragma unroll
+                    for (int c = 0; c < C; ++c) o_s[tt_of * CT + cg * C + c] = o_prev[c];
+                }
+            };
+            // a token's k (then q) is fetched as soon as the token before has used its own for the last time, so the
+            // shared-memory reads run beside the arithmetic
+            uint64_t kr[R / 2], qr[R / 2];
+            auto fetch = [&](uint64_t* dst, const ulonglong2* src, int tt_of) {
+#pragma unroll
+                for (int r = 0; r < R / 4; ++r) {
+                    const ulonglong2 t = src[tt_of * step4 + L * r];
+                    dst[2 * r] = t.x;
+                    dst[2 * r + 1] = t.y;
+                }
+            };
+            fetch(kr, k4, 0);
+            fetch(qr, q4, 0);
             for (int tt = 0; tt < nb; ++tt) {
-                float kr[R], qr[R];
+                const int next = min(tt + 1, nb - 1);
+                float v[C];
 #pragma unroll
-                for (int r = 0; r < R / 4; ++r) {
-                    const float4 kk = k4[tt * step4 + r];
-                    kr[4 * r] = kk.x; kr[4 * r + 1] = kk.y; kr[4 * r + 2] = kk.z; kr[4 * r + 3] = kk.w;
-                }
+                for (int c = 0; c < C; ++c) v[c] = vcol[tt * CT + c];
+                uint64_t o2[C];      // (sum over even rows, sum over odd rows)
 #pragma unroll
-                for (int r = 0; r < R / 4; ++r) {
-                    const float4 qq = q4[tt * step4 + r];
-                    qr[4 * r] = qq.x; qr[4 * r + 1] = qq.y; qr[4 * r + 2] = qq.z; qr[4 * r + 3] = qq.w;
-                }
-                const float v = s.v[tt * CT + col];
-                float o4[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int c = 0; c < C; ++c) o2[c] = 0ull;
                 if (MODE == MODE_DELTA) {
                     const float g = s.g[tt], beta = s.b[tt];
-                    float p4[4] = {0.f, 0.f, 0.f, 0.f};
+                    const uint64_t gg = pair_f32(g, g);
+                    uint64_t p2[C];
 #pragma unroll
-                    for (int r = 0; r < R; ++r) p4[r & 3] = fmaf(S[r], kr[r], p4[r & 3]);
-                    float p = (p4[0] + p4[1]) + (p4[2] + p4[3]);
-                    // the read-out of the token before is reduced beside this token's S^T k
-                    for (int off = 1; off < L; off <<= 1) {
-                        p += __shfl_xor_sync(0xffffffffu, p, off);
-                        o_prev += __shfl_xor_sync(0xffffffffu, o_prev, off);
+                    for (int c = 0; c < C; ++c) p2[c] = 0ull;
+#pragma unroll
+                    for (int m = 0; m < R / 2; ++m) {
+#pragma unroll
+                        for (int c = 0; c < C; ++c) p2[c] = fma_pair(S[c][m], kr[m], p2[c]);
                     }
-                    if (tt > 0 && kl == 0) o_s[(tt - 1) * CT + col] = o_prev;
-                    const float w = beta * (v - g * p);
+                    float p[C];
 #pragma unroll
-                    for (int r = 0; r < R; ++r) {
-                        S[r] = fmaf(kr[r], w, g * S[r]);
-                        o4[r & 3] = fmaf(S[r], qr[r], o4[r & 3]);
+                    for (int c = 0; c < C; ++c) {
+                        float even, oddp;
+                        unpair_f32(p2[c], even, oddp);
+                        p[c] = even + oddp;
+                    }
+                    reduce(tt - 1, true, p);
+                    uint64_t w[C];
+#pragma unroll
+                    for (int c = 0; c < C; ++c) {
+                        const float wc = beta * (v[c] - g * p[c]);
+                        w[c] = pair_f32(wc, wc);
+                    }
+#pragma unroll
+                    for (int m = 0; m < R / 2; ++m) {
+#pragma unroll
+                        for (int c = 0; c < C; ++c) S[c][m] = fma_pair(kr[m], w[c], mul_pair(gg, S[c][m]));
                     }
                 } else {
+                    const uint64_t ones = pair_f32(1.f, 1.f), neg = pair_f32(-1.f, -1.f);
+                    uint64_t vv[C];
 #pragma unroll
-                    for (int r = 0; r < R; ++r) {
-                        const float f = kr[r];
-                        S[r] = fmaf(f, S[r], (1.f - f) * v);
-                        o4[r & 3] = fmaf(S[r], qr[r], o4[r & 3]);
+                    for (int c = 0; c < C; ++c) vv[c] = pair_f32(v[c], v[c]);
+#pragma unroll
+                    for (int m = 0; m < R / 2; ++m) {
+                        const uint64_t f = kr[m], nf = fma_pair(f, neg, ones);      // 1 - f
+#pragma unroll
+                        for (int c = 0; c < C; ++c) S[c][m] = fma_pair(f, S[c][m], mul_pair(nf, vv[c]));
                     }
-                    for (int off = 1; off < L; off <<= 1) o_prev += __shfl_xor_sync(0xffffffffu, o_prev, off);
-                    if (tt > 0 && kl == 0) o_s[(tt - 1) * CT + col] = o_prev;
+                    if (tt > 0) reduce(tt - 1, false, nullptr);
                 }
-                o_prev = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+                fetch(kr, k4, next);
+#pragma unroll
+                for (int m = 0; m < R / 2; ++m) {
+#pragma unroll
+                    for (int c = 0; c < C; ++c) o2[c] = fma_pair(S[c][m], qr[m], o2[c]);
+                }
+                fetch(qr, q4, next);
+#pragma unroll
+                for (int c = 0; c < C; ++c) {
+                    float even, oddp;
+                    unpair_f32(o2[c], even, oddp);
+                    o_prev[c] = even + oddp;
+                }
             }
-            for (int off = 1; off < L; off <<= 1) o_prev += __shfl_xor_sync(0xffffffffu, o_prev, off);
-            if (kl == 0) o_s[(nb - 1) * CT + col] = o_prev;
+            reduce(nb - 1, false, nullptr);
             group_barrier(2, WALKERS);
             float* orow = a.out + (size_t)(t0 + b0) * (a.H * dv) + h * dv + c0;
             for (int idx = tid; idx < nb * CT; idx += WALKERS) {
@@ -325,16 +414,32 @@ __global__ __launch_bounds__(SPLIT ? THREADS : WALKERS, SPLIT ? 1 : 2) void matr
         }
         if (stager && b + 1 < batches) {
             const int nn = min(TB, n - b0 - TB);
-            if (one) stage_tokens<MODE, true>(a, stage_at((b + 1) & 1), ltid, h, hk, t0 + b0 + TB, nn, c0);
-            else stage_tokens<MODE, false>(a, stage_at((b + 1) & 1), ltid, h, hk, t0 + b0 + TB, nn, c0);
+            if (one) stage_tokens<MODE, true, R>(a, stage_at((b + 1) & 1), ltid, h, hk, t0 + b0 + TB, nn, c0);
+            else stage_tokens<MODE, false, R>(a, stage_at((b + 1) & 1), ltid, h, hk, t0 + b0 + TB, nn, c0);
         }
         __syncthreads();      // the walkers are done with this half and with o_s, the stagers have filled the other half
     }
-    if (live) {
+    if (walker) {
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const int i = kl * R + r;
-            if (i < d) st[(size_t)i * dv + j] = S[r];
+        for (int c = 0; c < C; ++c) {
+            const int j = c0 + cg * C + c;
+#pragma unroll
+            for (int m = 0; m < R / 4; ++m) {
+                const int i = 4 * (kl + L * m);
+                if (j < dv && i < d) {
+                    float4 t;
+                    unpair_f32(S[c][2 * m], t.x, t.y);
+                    unpair_f32(S[c][2 * m + 1], t.z, t.w);
+                    float* dst = st + (size_t)j * d + i;
+                    if (vec) *reinterpret_cast<float4*>(dst) = t;
+                    else {
+                        dst[0] = t.x;
+                        if (i + 1 < d) dst[1] = t.y;
+                        if (i + 2 < d) dst[2] = t.z;
+                        if (i + 3 < d) dst[3] = t.w;
+                    }
+                }
+            }
         }
     }
 }
@@ -366,16 +471,31 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, Rows gate, in
     }
 }
 
-int rnn_lanes(int d) {
-    int L = 1;
-    while (L * R < d) L <<= 1;
-    return L;
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <int MODE, int R, int C>
+int rnn_launch(RnnArgs a, bool split, dim3 grid, size_t smem, cudaStream_t stream) {
+    auto kern = split ? matrix_rnn_kernel<MODE, true, R, C> : matrix_rnn_kernel<MODE, false, R, C>;
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        vcb_set_error("matrix_rnn: %zu bytes of shared memory refused", smem);
+        return -2;
+    }
+    launch_pdl(kern, grid, dim3(split ? THREADS : WALKERS), smem, stream, a);
+    return 0;
 }
 
 }  // namespace
 
 // mode 0: the gated delta rule; 1: the gated linear form (see the head of this file).  u [S][T][ld] the projection's sums;
-// x [T][ldx] the convolved rows (mode 0).  state [slots][H][d][dv].  out [rows][H * dv] 32-bit, rows >= the entries' tokens.  Entries of no tokens are left out.
+// x [T][ldx] the convolved rows (mode 0).  state [slots][H][dv][d] (a value column's d rows in a run).  out [rows][H * dv] 32-bit, rows >= the entries' tokens.  Entries of no tokens are left out.
 VCB_API int vcb_matrix_rnn(int mode, const float* u, int S, long long s_stride, long long ld, const float* x, long long ldx,
                            int q_col, int k_col, int v_col, int b_col, int a_col, const float* dt_bias, const float* rate,
                            const float* f_bias, const float* lower, float* state, long long state_stride, const int* q_start,
@@ -383,27 +503,32 @@ VCB_API int vcb_matrix_rnn(int mode, const float* u, int S, long long s_stride, 
                            cudaStream_t stream) {
     if (E == 0) return 0;
     VCB_CHECK_ARG(mode == 0 || mode == 1, "matrix_rnn: unknown mode %d", mode);
-    VCB_CHECK_ARG(d >= 1 && d <= 32 * R, "matrix_rnn: %d state rows a head (1 to %d)", d, 32 * R);
+    VCB_CHECK_ARG(d >= 1 && d <= 512, "matrix_rnn: %d state rows a head (1 to 512)", d);
     VCB_CHECK_ARG(H >= 1 && G >= 1 && H % G == 0 && dv >= 1, "matrix_rnn: bad sizes H=%d G=%d dv=%d", H, G, dv);
     VCB_CHECK_ARG(H <= 65535 && E <= 65535, "matrix_rnn: %d heads, %d entries", H, E);
-    const int L = rnn_lanes(d), CT = WALKERS / L, DP = L * R;
+    VCB_CHECK_ARG(ld < (1 << 26) && ldx < (1 << 26), "matrix_rnn: rows of %lld and %lld lanes", ld, ldx);
+    const int R = d <= 64 ? 8 : 16;     // rows a thread keeps of a column
+    int L = 1;                          // lanes that share a column
+    while (L * R < d) L <<= 1;
+    // one column a thread while that gives no more blocks than there are SMs (a long portion of one request), else two
+    const long long blocks1 = (long long)((dv + WALKERS / L - 1) / (WALKERS / L)) * H * E;
+    const int C = blocks1 <= sm_count() ? 1 : 2;
+    const int CT = C * WALKERS / L, DP = L * R;
     const int TB = DP <= 256 ? 16 : 8;
     int dp_shift = 0, ct_shift = 0;
     while ((1 << dp_shift) < DP) ++dp_shift;
     while ((1 << ct_shift) < CT) ++ct_shift;
-    VCB_CHECK_ARG(ld < (1 << 26) && ldx < (1 << 26), "matrix_rnn: rows of %lld and %lld lanes", ld, ldx);
     RnnArgs a{Rows{u, S < 1 ? 1 : S, s_stride, ld}, x, ldx, q_col, k_col, v_col, b_col, a_col, dt_bias, rate, f_bias, lower, state,
               state_stride, q_start, q_len, slots, out, H, G, d, dv, L, TB, dp_shift, ct_shift};
-    const size_t smem = (size_t)(2 * (2 * TB * L * PAD + TB * CT + 2 * TB) + TB * CT) * sizeof(float);
+    const size_t smem = (size_t)(2 * (2 * TB * DP + TB * CT + 2 * TB) + TB * CT) * sizeof(float);
     const dim3 grid((dv + CT - 1) / CT, H, E);
     const bool split = rows > 4 * E;    // some entry has more than four tokens
-    auto kern = split ? (mode == 0 ? matrix_rnn_kernel<MODE_DELTA, true> : matrix_rnn_kernel<MODE_GATED, true>)
-                      : (mode == 0 ? matrix_rnn_kernel<MODE_DELTA, false> : matrix_rnn_kernel<MODE_GATED, false>);
-    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-        vcb_set_error("matrix_rnn: %zu bytes of shared memory refused", smem);
-        return -2;
-    }
-    launch_pdl(kern, grid, dim3(split ? THREADS : WALKERS), smem, stream, a);
+    int rc;
+#define VCB_RNN_GO(MODE_, R_) (C == 1 ? rnn_launch<MODE_, R_, 1>(a, split, grid, smem, stream) : rnn_launch<MODE_, R_, 2>(a, split, grid, smem, stream))
+    if (R == 8) rc = mode == 0 ? VCB_RNN_GO(MODE_DELTA, 8) : VCB_RNN_GO(MODE_GATED, 8);
+    else rc = mode == 0 ? VCB_RNN_GO(MODE_DELTA, 16) : VCB_RNN_GO(MODE_GATED, 16);
+#undef VCB_RNN_GO
+    if (rc != 0) return rc;
     VCB_CHECK_LAUNCH("matrix_rnn");
     return 0;
 }

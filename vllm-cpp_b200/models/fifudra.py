@@ -74,7 +74,7 @@ def describe_fifudra(cfg: FifudraConfig) -> ModelSpec:
         hidden_size=cfg.width, vocab_size=cfg.vocab, max_positions=cfg.max_positions, embed_tensor="embed",
         layers=tuple(layers), order=order, final_norm=norm, final_norm_prefix="final.norm", lm_head_tensor=None,
         embedding=PartSpec("token_embedding", {"tensor": "embed", "vocab_size": cfg.vocab, "hidden_size": cfg.width,
-                                               "scale": cfg.embedding_scale}))
+                                               "row_scale": cfg.embedding_scale}))
 
 
 register_architecture("Fifudra", FifudraConfig, describe_fifudra)

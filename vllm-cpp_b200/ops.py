@@ -1132,7 +1132,7 @@ def rope_rows(x, positions, freq, gain, out, *, heads, dims, width, in_head_stri
 
 def matrix_rnn(mode, u, state, q_start, q_len, slots, n_entries, out, *, heads, d, dv, q_col, k_col, v_col, x=None,
                kv_heads=None, b_col=0, a_col=0, dt_bias=None, rate=None, f_bias=None, lower=None):
-    """A recurrence over each entry's tokens whose state is ``state`` [slots, heads, d, dv] (32-bit), ``out`` [T, heads dv].
+    """A recurrence over each entry's tokens whose state S [d, dv] per head lies in ``state`` [slots, heads, dv, d] (32-bit, a value column's rows in a run), ``out`` [T, heads dv].
 
     ``mode`` "delta": S <- g S; w = beta (v - S^T k); S <- S + k w^T; o = S^T q.  q, k, v are columns ``q_col``,
     ``k_col``, ``v_col`` of ``x`` [T, C] (32-bit, convolved and activated; q and k of ``kv_heads`` heads, made unit
@@ -1141,7 +1141,7 @@ def matrix_rnn(mode, u, state, q_start, q_len, slots, n_entries, out, *, heads, 
     sigmoid(u[:, k_col ...] + f_bias), v = u[:, v_col ...].  ``u``: the projection's 32-bit sums ([S, T, C] partials)."""
     S, ss, ld = _rows_in(u, "u")
     _need(state, "state", torch.float32, contiguous=False); _need(out, "out", torch.float32)
-    assert state.shape[1:] == (heads, d, dv) and state[0].is_contiguous() and out.shape[1] == heads * dv
+    assert state.shape[1:] == (heads, dv, d) and state[0].is_contiguous() and out.shape[1] == heads * dv
     m = {"delta": 0, "gated": 1}[mode]
     ldx = 0
     if m == 0:

@@ -40,13 +40,13 @@ class Head(Part):
 
 
 class TokenEmbedding(Embedding):
-    """params: ``tensor`` (checkpoint name of the table), ``vocab_size``, ``hidden_size``; optional ``scale`` (default 1):
+    """params: ``tensor`` (checkpoint name of the table), ``vocab_size``, ``hidden_size``; optional ``row_scale`` (default 1):
     a constant on the gathered row (a tied head reads the table itself, without it)."""
 
     def __init__(self, params, prefix, build):
         super().__init__(params, prefix, build)
         self.name, self.vocab, self.hidden = str(params["tensor"]), int(params["vocab_size"]), int(params["hidden_size"])
-        self.scale = float(params.get("scale", 1.0))
+        self.scale = float(params.get("row_scale", 1.0))
         self.table = None
 
     def tensor_specs(self):

@@ -64,7 +64,7 @@ class DeltaRuleMixer(_MatrixStateMixer):
         self.w_in = self.w_o = self.conv_w = self.dt_bias = self.rate = self.norm_w = None
 
     def cache_spec(self):
-        state = CacheSpec("state", shape=(self.heads, self.d, self.dv), dtype="float32")
+        state = CacheSpec("state", shape=(self.heads, self.dv, self.d), dtype="float32")
         if self.taps > 1:
             return (state, CacheSpec("state", shape=(self.taps - 1, self.conv_channels), dtype="float32"))
         return state
@@ -118,7 +118,7 @@ class GatedLinearMixer(_MatrixStateMixer):
         self.w_in = self.w_o = self.f_bias = self.lower = self.norm_w = None
 
     def cache_spec(self):
-        return CacheSpec("state", shape=(self.heads, self.d, self.dv), dtype="float32")
+        return CacheSpec("state", shape=(self.heads, self.dv, self.d), dtype="float32")
 
     def tensor_specs(self):
         p, H = self.prefix, self.hidden
