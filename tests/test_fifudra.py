@@ -515,7 +515,8 @@ def test_latent_norms_rotation_and_store(dtype, q_rank, kv_rank, rot, S, scaling
 
 @gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,H,n_in,n_out,S", [(1, 3, 8, 12, 1), (9, 5, 6, 9, 2), (20, 2, 96, 80, 1), (17, 6, 33, 130, 3)])
+@pytest.mark.parametrize("T,H,n_in,n_out,S", [(1, 3, 8, 12, 1), (9, 5, 6, 9, 2), (20, 2, 96, 80, 1), (17, 6, 33, 130, 3),
+                                          (70, 3, 96, 80, 1), (130, 2, 12, 150, 2), (64, 2, 128, 96, 1), (97, 2, 30, 20, 1)])       # (long steps: a tile of tokens a block)
 def test_a_small_matrix_per_head_and_the_rotation_of_a_slice(dtype, T, H, n_in, n_out, S):
     """Every head's lanes, found at a stride and an offset, meet the head's own matrix; beside them a slice of every head
     is rotated into place."""

@@ -228,6 +228,59 @@ VCB_API int vcb_latent_norm_rope_store(const float* u, int S, long long s_stride
     return 0;
 }
 
+// The same for a long step: one block is head h and HT_TOKENS tokens, a thread an output lane.  The thread walks its row of
+// the matrix once (16 or 8 bytes at a time) and every token of the tile takes its sum from that pass, reading the token's
+// inputs as 16-byte words that all threads share.  n_in is a multiple of four.
+constexpr int HT_TOKENS = 32;
+
+__global__ __launch_bounds__(128) void head_linear_tile_kernel(HeadLinearArgs a) {
+    extern __shared__ __align__(16) float xt_s[];       // [HT_TOKENS][n_in]
+    pdl_trigger();
+    pdl_wait();
+    const int h = blockIdx.y, t0 = blockIdx.x * HT_TOKENS;
+    const int nt = min(HT_TOKENS, a.T - t0);
+    for (int i = threadIdx.x; i < HT_TOKENS * a.n_in; i += blockDim.x) {
+        const int tt = i / a.n_in, c = i % a.n_in;
+        float v = 0.f;
+        if (tt < nt) {
+            const size_t at = (size_t)(t0 + tt) * a.ld_in + (size_t)h * a.in_head_stride + a.in_off + c;
+            if (a.in_dtype == VCB_F32) {
+                for (int s = 0; s < a.S; ++s) v += ((const float*)a.in)[at + (size_t)s * a.s_stride];
+            } else {
+                v = __bfloat162float(((const __nv_bfloat16*)a.in)[at]);
+            }
+        }
+        xt_s[i] = v;
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < a.n_out; j += blockDim.x) {
+        float acc[HT_TOKENS];
+#pragma unroll
+        for (int tt = 0; tt < HT_TOKENS; ++tt) acc[tt] = 0.f;
+        const size_t mrow = ((size_t)h * a.n_out + j) * a.n_in;
+        for (int c = 0; c < a.n_in; c += 4) {
+            float4 w;
+            if (a.m_dtype == VCB_F32) {
+                w = *reinterpret_cast<const float4*>((const float*)a.m + mrow + c);
+            } else {
+                const uint2 raw = *reinterpret_cast<const uint2*>((const __nv_bfloat16*)a.m + mrow + c);
+                const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+                const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+                w = make_float4(lo.x, lo.y, hi.x, hi.y);
+            }
+#pragma unroll
+            for (int tt = 0; tt < HT_TOKENS; ++tt) {
+                const float4 x = *reinterpret_cast<const float4*>(xt_s + tt * a.n_in + c);
+                acc[tt] = fmaf(w.w, x.w, fmaf(w.z, x.z, fmaf(w.y, x.y, fmaf(w.x, x.x, acc[tt]))));
+            }
+        }
+#pragma unroll
+        for (int tt = 0; tt < HT_TOKENS; ++tt)
+            if (tt < nt)
+                store_from_f32(a.out, a.out_dtype, (size_t)(t0 + tt) * a.ld_out + (size_t)h * a.out_head_stride + a.out_off + j, acc[tt]);
+    }
+}
+
 VCB_API int vcb_head_linear(const void* in, int in_dtype, int S, long long s_stride, long long ld_in, int in_head_stride, int in_off,
                             const void* m, int m_dtype, void* out, int out_dtype, long long ld_out, int out_head_stride,
                             int out_off, int T, int H, int n_in, int n_out, cudaStream_t stream) {
@@ -238,6 +291,12 @@ VCB_API int vcb_head_linear(const void* in, int in_dtype, int S, long long s_str
     VCB_CHECK_ARG(H <= 65535, "head_linear: %d heads", H);
     HeadLinearArgs a{in, in_dtype, S < 1 ? 1 : S, s_stride, ld_in, in_head_stride, in_off, m, m_dtype, out, out_dtype, ld_out,
                      out_head_stride, out_off, T, H, n_in, n_out};
+    const size_t tile_smem = (size_t)HT_TOKENS * n_in * sizeof(float);
+    if (T >= 2 * HT_TOKENS && (n_in & 3) == 0 && tile_smem <= 48 * 1024 && (reinterpret_cast<uintptr_t>(m) & 15) == 0) {
+        launch_pdl(head_linear_tile_kernel, dim3((T + HT_TOKENS - 1) / HT_TOKENS, H), dim3(128), tile_smem, stream, a);
+        VCB_CHECK_LAUNCH("head_linear");
+        return 0;
+    }
     launch_pdl(head_linear_kernel, dim3((T + HL_TOKENS - 1) / HL_TOKENS, H), dim3(256), smem, stream, a);
     VCB_CHECK_LAUNCH("head_linear");
     return 0;
