@@ -79,6 +79,70 @@ __global__ void hyper_mix_norm_kernel(HyperArgs a) {
     const int t = a.rows != nullptr ? a.rows[blockIdx.x] : blockIdx.x;
     const size_t plane = (size_t)a.T * W;
     float ss = 0.f;
+    // rows of a multiple of four lanes on 16-byte boundaries move as 16-byte words (the same sums, lane by lane)
+    auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const bool vec = (W & 3) == 0 && aligned16(a.streams) && aligned16(a.init) && aligned16(a.gain) && aligned16(a.out) && aligned16(u_s) &&
+                     aligned16(a.y.p) && (a.y.ld & 3) == 0 && (a.y.s_stride & 3) == 0;
+    if (vec) {
+        const int W4 = W >> 2;
+        for (int c4 = threadIdx.x; c4 < W4; c4 += blockDim.x) {
+            float4 x[MAX_STREAMS];
+            if (a.init != nullptr) {
+                const float4 v = reinterpret_cast<const float4*>(a.init + (size_t)t * W)[c4];
+#pragma unroll
+                for (int s = 0; s < MAX_STREAMS; ++s) x[s] = v;
+            } else {
+#pragma unroll
+                for (int s = 0; s < MAX_STREAMS; ++s)
+                    if (s < S) x[s] = reinterpret_cast<const float4*>(a.streams + s * plane + (size_t)t * W)[c4];
+            }
+            float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (a.y.p != nullptr) {
+                float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+                const float* yp = a.y.p + (long long)t * a.y.ld;
+                for (int k = 0; k < a.y.S; ++k) {
+                    const float4 part = reinterpret_cast<const float4*>(yp + (long long)k * a.y.s_stride)[c4];
+                    y.x += part.x; y.y += part.y; y.z += part.z; y.w += part.w;
+                }
+#pragma unroll
+                for (int r = 0; r < MAX_STREAMS; ++r) {
+                    if (r < S) {
+                        float4 n = make_float4(co[r] * y.x, co[r] * y.y, co[r] * y.z, co[r] * y.w);
+#pragma unroll
+                        for (int s2 = 0; s2 < MAX_STREAMS; ++s2)
+                            if (s2 < S) {
+                                const float m = cm[s2 * S + r];
+                                n.x = fmaf(m, x[s2].x, n.x); n.y = fmaf(m, x[s2].y, n.y); n.z = fmaf(m, x[s2].z, n.z); n.w = fmaf(m, x[s2].w, n.w);
+                            }
+                        if (a.rows == nullptr) reinterpret_cast<float4*>(a.streams + r * plane + (size_t)t * W)[c4] = n;
+                        u.x = fmaf(ci[r], n.x, u.x); u.y = fmaf(ci[r], n.y, u.y); u.z = fmaf(ci[r], n.z, u.z); u.w = fmaf(ci[r], n.w, u.w);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < MAX_STREAMS; ++r) {
+                    if (r < S) {
+                        if (a.init != nullptr && a.rows == nullptr) reinterpret_cast<float4*>(a.streams + r * plane + (size_t)t * W)[c4] = x[r];
+                        u.x = fmaf(ci[r], x[r].x, u.x); u.y = fmaf(ci[r], x[r].y, u.y); u.z = fmaf(ci[r], x[r].z, u.z); u.w = fmaf(ci[r], x[r].w, u.w);
+                    }
+                }
+            }
+            reinterpret_cast<float4*>(u_s)[c4] = u;
+            ss = fmaf(u.w, u.w, fmaf(u.z, u.z, fmaf(u.y, u.y, fmaf(u.x, u.x, ss))));
+        }
+        if (a.gain == nullptr) return;
+        ss = block_sum(ss, red);
+        const float rstd = rsqrtf(ss / (float)W + a.eps);
+        TOUT* o = (TOUT*)a.out + (size_t)blockIdx.x * W;
+        for (int c4 = threadIdx.x; c4 < W4; c4 += blockDim.x) {
+            const float4 u = reinterpret_cast<const float4*>(u_s)[c4], g = reinterpret_cast<const float4*>(a.gain)[c4];
+            o[4 * c4] = from_f32<TOUT>(u.x * rstd * g.x);
+            o[4 * c4 + 1] = from_f32<TOUT>(u.y * rstd * g.y);
+            o[4 * c4 + 2] = from_f32<TOUT>(u.z * rstd * g.z);
+            o[4 * c4 + 3] = from_f32<TOUT>(u.w * rstd * g.w);
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
         float x[MAX_STREAMS];
         if (a.init != nullptr) {
