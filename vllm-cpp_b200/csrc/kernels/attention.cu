@@ -16,9 +16,10 @@
 // is then [nkv][page_size][hd] keys followed by [nkv][page_size][hd_v] values); the
 // scaled score may be capped, s <- c tanh(s / c), before a per-head slope times the
 // distance, slope_h (pos - j), is taken off it; and the softmax may have a sink, a
-// silent key of score 0 without a value: w_j = exp(s_j) / (1 + sum_j exp(s_j)).  The
-// sink enters as the starting state (maximum 0, sum 1) of the item's first key slice,
-// so sliced items merge as they are.
+// silent key without a value, of score 0 or of a learned score per head that is not
+// scaled: w_j = exp(s_j) / (exp(sink_h) + sum_j exp(s_j)).  The sink enters as the
+// starting state (maximum sink_h, sum 1) of the item's first key slice, so sliced
+// items merge as they are.
 // Items whose key range is sliced write (max, sum, unnormalised output) partials,
 // merged by attn_merge_kernel in slice order.
 #include "common.cuh"
@@ -60,6 +61,7 @@ struct AttnArgs {
     float softcap;
     const float* slope;
     int sink;
+    const float* sink_value;    // with a sink: its score per head (null: 0); it is not scaled
 };
 
 template <typename T> struct Vec8;
@@ -155,9 +157,9 @@ __global__ __launch_bounds__(TK) void attn_paged_kernel(AttnArgs a) {
     }
     if (tid < RMAX) {
         const bool with_sink = a.sink && slice == 0;
-        m_s[tid] = with_sink ? 0.f : -CUDART_INF_F;
-        l_s[tid] = with_sink ? 1.f : 0.f;
         const int h = head0 + tid % gq;
+        m_s[tid] = with_sink ? (a.sink_value != nullptr && tid < R ? a.sink_value[h] : 0.f) : -CUDART_INF_F;
+        l_s[tid] = with_sink ? 1.f : 0.f;
         da_s[tid] = a.dist_a != nullptr && tid < R ? a.dist_a[h] : (a.slope != nullptr && tid < R ? a.slope[h] : 0.f);
         db_s[tid] = a.dist_a != nullptr && tid < R ? a.dist_b[h] : 0.f;
     }
@@ -373,7 +375,7 @@ VCB_API int vcb_attn_paged_ex(const void* q, void* out, int dtype, const void* p
                               const int* ctx_len, const int* items, int n_items, int rows_max, float* part_o,
                               float* part_ml, int nh, int nkv, int hd, int page_size, int num_pages, int window,
                               float scale, int keep_first, const float* dist_a, const float* dist_b, int hd_v,
-                              float softcap, const float* slope, int sink, int* status, cudaStream_t stream) {
+                              float softcap, const float* slope, int sink, const float* sink_value, int* status, cudaStream_t stream) {
     if (n_items == 0) return 0;
     if (hd_v <= 0) hd_v = hd;
     VCB_CHECK_ARG(nh > 0 && nkv > 0 && nh % nkv == 0, "attn_paged: %d query heads are not a multiple of %d KV heads", nh, nkv);
@@ -388,7 +390,7 @@ VCB_API int vcb_attn_paged_ex(const void* q, void* out, int dtype, const void* p
     VCB_CHECK_ARG(softcap >= 0.f, "attn_paged: a negative cap");
     AttnArgs a{q, out, pages, page_stride, block_table, table_row, max_blocks, q_start, q_len, ctx_len, items, part_o, part_ml,
                nh, nkv, hd, page_size, num_pages, window, scale, status, 0, 0, keep_first, dist_a, dist_b, hd_v,
-               softcap, slope, sink};
+               softcap, slope, sink, sink_value};
     if (dtype == VCB_F32) return rows_max == 8 ? launch_attn<float, 8>(a, n_items, stream) : launch_attn<float, 32>(a, n_items, stream);
     return rows_max == 8 ? launch_attn<__nv_bfloat16, 8>(a, n_items, stream) : launch_attn<__nv_bfloat16, 32>(a, n_items, stream);
 }

@@ -539,7 +539,7 @@ __global__ void bias_act_vec_kernel(RowsIn in, TOUT* __restrict__ out, int T, in
             if (kind == 0) f[k] = 0.5f * x * (1.f + erff(x * 0.70710678118654752440f));
             else if (kind == 1) f[k] = 0.5f * x * (1.f + tanhf(0.79788456080286535588f * (x + 0.044715f * x * x * x)));
             else if (kind == 2) f[k] = x / (1.f + expf(-x));
-            else { const float r = fmaxf(x, 0.f); f[k] = r * r; }
+            else if (kind == 3) { const float r = fmaxf(x, 0.f); f[k] = r * r; }
         }
         store4<TOUT>(out + (size_t)t * (4 * (size_t)C4) + c, z);
     }
@@ -557,7 +557,8 @@ __global__ void bias_act_kernel(RowsIn in, TOUT* __restrict__ out, long long tot
         if (kind == 0) r = 0.5f * z * (1.f + erff(z * 0.70710678118654752440f));
         else if (kind == 1) r = 0.5f * z * (1.f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
         else if (kind == 2) r = z / (1.f + expf(-z));
-        else { const float p = fmaxf(z, 0.f); r = p * p; }
+        else if (kind == 3) { const float p = fmaxf(z, 0.f); r = p * p; }
+        else r = z;
         out[i] = from_f32<TOUT>(r);
     }
 }
@@ -713,11 +714,11 @@ VCB_API int vcb_gated_norm_add(float* resid, const float* y, int Sy, long long y
     return 0;
 }
 
-// kind 0: GELU with erf, 1: GELU with tanh, 2: SiLU, 3: the square of ReLU
+// kind 0: GELU with erf, 1: GELU with tanh, 2: SiLU, 3: the square of ReLU, 4: none (the sums, plus bias, in out_dtype)
 VCB_API int vcb_bias_act(const float* in, int S, long long s_stride, long long ld, const float* bias, void* out, int out_dtype,
                          int T, int C, int kind, cudaStream_t stream) {
     if (T == 0 || C == 0) return 0;
-    VCB_CHECK_ARG(kind >= 0 && kind <= 3, "bias_act: unknown activation %d", kind);
+    VCB_CHECK_ARG(kind >= 0 && kind <= 4, "bias_act: unknown activation %d", kind);
     RowsIn r{in, S < 1 ? 1 : S, s_stride, ld, bias};
     const long long total = (long long)T * C;
     if (C % 4 == 0 && rows_vec_ok(r) && (uintptr_t)out % 16 == 0) {

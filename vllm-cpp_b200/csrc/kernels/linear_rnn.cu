@@ -5,6 +5,12 @@
 //                            q times d^(-1/2); beta = sigmoid(b); g = exp(-rate_h softplus(a + dt_bias_h))
 //  * the gated linear form   S <- diag(f) S + (1 - f) v^T;  o = S^T q
 //                            q = silu(.), f = low + (1 - low) sigmoid(. + bias), all from one row of 32-bit sums
+//  * the decayed form        S <- diag(f) S + k v^T;  o = S^T q
+//                            q times d^(-1/2), k, v from one row of 32-bit sums; f = sigmoid(z + bias)^(1/tau) per state row,
+//                            z the sums of a second (low-rank) projection: exp(-softplus(-(z + bias)) / tau) in 32-bit
+//  * retention               S <- decay_h S + k v^T;  o = S^T q
+//                            one fixed decay per head; the first `rot` lanes of q and k turned by position * freq[i]
+//                            (pairs in halves or interleaved), k then times d^(-1/2)
 //  * head_norm_gate          every head of o divided by its root mean square, times a gain shared by the heads, times
 //                            silu(gate) where there is a gate
 //
@@ -82,7 +88,7 @@ __device__ __forceinline__ uint64_t mul_pair(uint64_t x, uint64_t y) {
 }
 __device__ __forceinline__ void group_barrier(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
 
-enum { MODE_DELTA = 0, MODE_GATED = 1 };
+enum { MODE_DELTA = 0, MODE_GATED = 1, MODE_DECAYED = 2, MODE_RETAIN = 3 };
 
 struct RnnArgs {
     Rows u;                 // the projection's sums
@@ -103,11 +109,18 @@ struct RnnArgs {
     float* out;             // [T][H * dv]
     int H, G, d, dv, L;     // G heads of q and k (MODE_DELTA; head h reads h / (H / G))
     int TB, dp_shift, ct_shift;     // tokens staged at a time; log2(L * R); log2(value columns a block owns)
+    Rows z;                 // MODE_DECAYED: the decay's sums [T][H * d]; f_bias is their bias
+    float inv_tau;          // MODE_DECAYED: 1 / tau
+    const float* decay;     // MODE_RETAIN: [H]
+    const int* ctx_len;     // MODE_RETAIN: an entry's tokens end at this position
+    const float* freq;      // MODE_RETAIN: [rot / 2]
+    int rot, interleaved;   // MODE_RETAIN: lanes of q and k that turn, and how they pair
 };
 
 struct Stage {              // one half of the double buffer
     float* q;               // [TB][L * R]
     float* k;               // [TB][L * R]   (MODE_GATED: the forget gate)
+    float* f;               // [TB][L * R]   (MODE_DECAYED only: the decay of every state row)
     float* v;               // [TB][CT]
     float* g;               // [TB]
     float* b;               // [TB]
@@ -119,7 +132,7 @@ struct Stage {              // one half of the double buffer
 // (ONE: the sums are one slice, so a load has no add behind it.)
 template <int MODE, bool ONE, int R>
 __device__ __forceinline__ void stage_tokens(const RnnArgs& a, const Stage& s, int ltid, int h, int hk, long long t_first, int nb,
-                                             int c0) {
+                                             int c0, int pos_first) {
     const int d = a.d, dv = a.dv, DP = 1 << a.dp_shift, DPP = DP, CT = 1 << a.ct_shift, TB = a.TB;
     const int ldx = (int)a.ldx, ldu = (int)a.u.ld;
     // v, beta and the decay first: their loads fly while q and k are fetched
@@ -155,14 +168,17 @@ __device__ __forceinline__ void stage_tokens(const RnnArgs& a, const Stage& s, i
                 fb = a.f_bias[h * d + i];
             }
         }
+        if (MODE == MODE_DECAYED && in) fb = a.f_bias[h * d + i];
+        const float dscale = rsqrtf((float)d);
         const int ldq = MODE == MODE_DELTA ? ldx : ldu;
         for (int tb = tt0; tb < TB; tb += U * tpr) {
-            float qv[U], kv[U];
+            float qv[U], kv[U], fv[MODE == MODE_DECAYED ? U : 1];
 #pragma unroll
             for (int w = 0; w < U; ++w) {
                 const int tt = tb + w * tpr;
                 qv[w] = 0.f;
                 kv[w] = 0.f;
+                if constexpr (MODE == MODE_DECAYED) fv[w] = 0.f;
                 if (in && tt < nb) {
                     if (MODE == MODE_DELTA || ONE) {
                         qv[w] = qp[tt * ldq];
@@ -171,6 +187,7 @@ __device__ __forceinline__ void stage_tokens(const RnnArgs& a, const Stage& s, i
                         qv[w] = rows_at(a.u, t_first + tt, a.q_col + h * d + i);
                         kv[w] = rows_at(a.u, t_first + tt, a.k_col + h * d + i);
                     }
+                    if constexpr (MODE == MODE_DECAYED) fv[w] = rows_at(a.z, t_first + tt, h * d + i);
                 }
             }
 #pragma unroll
@@ -181,6 +198,12 @@ __device__ __forceinline__ void stage_tokens(const RnnArgs& a, const Stage& s, i
                         qv[w] = silu_f(qv[w]);
                         kv[w] = low + (1.f - low) * sigmoid_f(kv[w] + fb);
                     }
+                    if constexpr (MODE == MODE_DECAYED) {
+                        qv[w] *= dscale;
+                        // sigmoid(x)^(1/tau) = exp(-softplus(-x) / tau); rows beyond d keep a zero state whatever they hold
+                        s.f[tt * DPP + pi] = in && tt < nb ? expf(-softplus_f(-(fv[w] + fb)) * a.inv_tau) : 0.f;
+                    }
+                    if (MODE == MODE_RETAIN && i >= a.rot) kv[w] *= dscale;     // (the turning lanes after their turn)
                     s.q[tt * DPP + pi] = qv[w];
                     s.k[tt * DPP + pi] = kv[w];
                 }
@@ -219,6 +242,25 @@ __device__ __forceinline__ void stage_tokens(const RnnArgs& a, const Stage& s, i
             }
         }
     }
+    if (MODE == MODE_RETAIN && a.rot > 0) {
+        group_barrier(1, STAGERS);
+        // q and k turned by the token's position, a thread a pair of lanes; k then times d^(-1/2)
+        const int hr = a.rot >> 1;
+        const float kscale = rsqrtf((float)d);
+        for (int idx = ltid; idx < nb * hr; idx += STAGERS) {
+            const int tt = idx / hr, i = idx % hr;
+            const int la = a.interleaved ? 2 * i : i, lb = a.interleaved ? 2 * i + 1 : i + hr;
+            float sn, cs;
+            sincosf((float)(pos_first + tt) * a.freq[i], &sn, &cs);
+            float* q = s.q + tt * DPP;
+            float* k = s.k + tt * DPP;
+            const float qa = q[la], qb = q[lb], ka = k[la], kb = k[lb];
+            q[la] = qa * cs - qb * sn;
+            q[lb] = qb * cs + qa * sn;
+            k[la] = (ka * cs - kb * sn) * kscale;
+            k[lb] = (kb * cs + ka * sn) * kscale;
+        }
+    }
 }
 
 // SPLIT: 512 threads, stagers beside walkers (long portions).  Otherwise 256 threads that stage and then walk, several blocks
@@ -235,12 +277,14 @@ __global__ __launch_bounds__(SPLIT ? THREADS : WALKERS, SPLIT ? 1 : 2) void matr
     if (n <= 0) return;
     const int L = a.L, CT = 1 << a.ct_shift, DPP = L * R, TB = a.TB;
     const int d = a.d, dv = a.dv;
-    const int half = 2 * TB * DPP + TB * CT + 2 * TB;       // (a multiple of four lanes)
+    constexpr int NQK = MODE == MODE_DECAYED ? 3 : 2;
+    const int half = NQK * TB * DPP + TB * CT + 2 * TB;       // (a multiple of four lanes)
     auto stage_at = [&](int which) {
         Stage s;
         s.q = sm + which * half;
         s.k = s.q + TB * DPP;
-        s.v = s.k + TB * DPP;
+        s.f = s.k + TB * DPP;
+        s.v = s.q + NQK * TB * DPP;
         s.g = s.v + TB * CT;
         s.b = s.g + TB;
         return s;
@@ -254,7 +298,8 @@ __global__ __launch_bounds__(SPLIT ? THREADS : WALKERS, SPLIT ? 1 : 2) void matr
     const int c0 = blockIdx.x * CT;
     const long long t0 = a.q_start[e];
     const int hk = MODE == MODE_DELTA ? h / (a.H / a.G) : h;
-    const bool one = a.u.S == 1;
+    const bool one = a.u.S == 1 && (MODE != MODE_DECAYED || a.z.S == 1);
+    const int pos0 = MODE == MODE_RETAIN ? a.ctx_len[e] - n : 0;       // position of the entry's first token
     float* st = a.state + (size_t)a.slots[e] * a.state_stride + (size_t)h * d * dv;     // [dv][d]: a column's rows in a run
     // this thread's rows: the pieces of four 4 (kl + L m) .. + 3, m < R / 4, so that the L threads of a column read
     // neighbouring 16-byte words of q, k and the state.  Pairs of rows in a 64-bit register: the multiply-adds run on pairs.
@@ -284,8 +329,8 @@ __global__ __launch_bounds__(SPLIT ? THREADS : WALKERS, SPLIT ? 1 : 2) void matr
     }
     const int batches = (n + TB - 1) / TB;
     if (stager) {
-        if (one) stage_tokens<MODE, true, R>(a, stage_at(0), ltid, h, hk, t0, min(TB, n), c0);
-        else stage_tokens<MODE, false, R>(a, stage_at(0), ltid, h, hk, t0, min(TB, n), c0);
+        if (one) stage_tokens<MODE, true, R>(a, stage_at(0), ltid, h, hk, t0, min(TB, n), c0, pos0);
+        else stage_tokens<MODE, false, R>(a, stage_at(0), ltid, h, hk, t0, min(TB, n), c0, pos0);
     }
     __syncthreads();
     for (int b = 0; b < batches; ++b) {
@@ -295,6 +340,7 @@ __global__ __launch_bounds__(SPLIT ? THREADS : WALKERS, SPLIT ? 1 : 2) void matr
             const Stage s = stage_at(b & 1);
             const ulonglong2* q4 = reinterpret_cast<const ulonglong2*>(s.q) + kl;
             const ulonglong2* k4 = reinterpret_cast<const ulonglong2*>(s.k) + kl;
+            const ulonglong2* f4 = reinterpret_cast<const ulonglong2*>(s.f) + kl;
             const float* vcol = s.v + cg * C;
             const int step4 = DPP / 4;
             const bool odd = kl & 1;
@@ -328,7 +374,7 @@ __global__ __launch_bounds__(SPLIT ? THREADS : WALKERS, SPLIT ? 1 : 2) void matr
             };
             // a token's k (then q) is fetched as soon as the token before has used its own for the last time, so the
             // shared-memory reads run beside the arithmetic
-            uint64_t kr[R / 2], qr[R / 2];
+            uint64_t kr[R / 2], qr[R / 2], fr[MODE == MODE_DECAYED ? R / 2 : 1];
             auto fetch = [&](uint64_t* dst, const ulonglong2* src, int tt_of) {
 #pragma unroll
                 for (int r = 0; r < R / 4; ++r) {
@@ -339,6 +385,8 @@ __global__ __launch_bounds__(SPLIT ? THREADS : WALKERS, SPLIT ? 1 : 2) void matr
             };
             fetch(kr, k4, 0);
             fetch(qr, q4, 0);
+            if constexpr (MODE == MODE_DECAYED) fetch(fr, f4, 0);
+            const float head_decay = MODE == MODE_RETAIN ? a.decay[h] : 0.f;
             for (int tt = 0; tt < nb; ++tt) {
                 const int next = min(tt + 1, nb - 1);
                 float v[C];
@@ -347,7 +395,7 @@ __global__ __launch_bounds__(SPLIT ? THREADS : WALKERS, SPLIT ? 1 : 2) void matr
                 uint64_t o2[C];      // (sum over even rows, sum over odd rows)
 #pragma unroll
                 for (int c = 0; c < C; ++c) o2[c] = 0ull;
-                if (MODE == MODE_DELTA) {
+                if constexpr (MODE == MODE_DELTA) {
                     const float g = s.g[tt], beta = s.b[tt];
                     const uint64_t gg = pair_f32(g, g);
                     uint64_t p2[C];
@@ -377,6 +425,19 @@ __global__ __launch_bounds__(SPLIT ? THREADS : WALKERS, SPLIT ? 1 : 2) void matr
 #pragma unroll
                         for (int c = 0; c < C; ++c) S[c][m] = fma_pair(kr[m], w[c], mul_pair(gg, S[c][m]));
                     }
+                } else if constexpr (MODE == MODE_DECAYED || MODE == MODE_RETAIN) {
+                    const uint64_t gg = pair_f32(head_decay, head_decay);
+                    uint64_t vv[C];
+#pragma unroll
+                    for (int c = 0; c < C; ++c) vv[c] = pair_f32(v[c], v[c]);
+#pragma unroll
+                    for (int m = 0; m < R / 2; ++m) {
+                        const uint64_t f = MODE == MODE_DECAYED ? fr[MODE == MODE_DECAYED ? m : 0] : gg;
+#pragma unroll
+                        for (int c = 0; c < C; ++c) S[c][m] = fma_pair(kr[m], vv[c], mul_pair(f, S[c][m]));
+                    }
+                    if (tt > 0) reduce(tt - 1, false, nullptr);
+                    if constexpr (MODE == MODE_DECAYED) fetch(fr, f4, next);
                 } else {
                     const uint64_t ones = pair_f32(1.f, 1.f), neg = pair_f32(-1.f, -1.f);
                     uint64_t vv[C];
@@ -414,8 +475,8 @@ __global__ __launch_bounds__(SPLIT ? THREADS : WALKERS, SPLIT ? 1 : 2) void matr
         }
         if (stager && b + 1 < batches) {
             const int nn = min(TB, n - b0 - TB);
-            if (one) stage_tokens<MODE, true, R>(a, stage_at((b + 1) & 1), ltid, h, hk, t0 + b0 + TB, nn, c0);
-            else stage_tokens<MODE, false, R>(a, stage_at((b + 1) & 1), ltid, h, hk, t0 + b0 + TB, nn, c0);
+            if (one) stage_tokens<MODE, true, R>(a, stage_at((b + 1) & 1), ltid, h, hk, t0 + b0 + TB, nn, c0, pos0 + b0 + TB);
+            else stage_tokens<MODE, false, R>(a, stage_at((b + 1) & 1), ltid, h, hk, t0 + b0 + TB, nn, c0, pos0 + b0 + TB);
         }
         __syncthreads();      // the walkers are done with this half and with o_s, the stagers have filled the other half
     }
@@ -465,7 +526,7 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, Rows gate, in
     ss = warp_sum(ss);
     const float rstd = rsqrtf(ss / (float)dv + eps);
     for (int c = lane; c < dv; c += 32) {
-        float v = o[base + c] * rstd * w[c];
+        float v = o[base + c] * rstd * (w != nullptr ? w[c] : 1.f);
         if (gate.p != nullptr) v *= silu_f(rows_at(gate, t, gate_col + h * dv + c));
         out[base + c] = from_f32<TOUT>(v);
     }
@@ -494,15 +555,21 @@ int rnn_launch(RnnArgs a, bool split, dim3 grid, size_t smem, cudaStream_t strea
 
 }  // namespace
 
-// mode 0: the gated delta rule; 1: the gated linear form (see the head of this file).  u [S][T][ld] the projection's sums;
-// x [T][ldx] the convolved rows (mode 0).  state [slots][H][dv][d] (a value column's d rows in a run).  out [rows][H * dv] 32-bit, rows >= the entries' tokens.  Entries of no tokens are left out.
+// mode 0: the gated delta rule; 1: the gated linear form; 2: the decayed form; 3: retention (see the head of this file).
+// u [S][T][ld] the projection's sums; x [T][ldx] the convolved rows (mode 0); z [zS][T][zld] the decay's sums (mode 2).
+// state [slots][H][dv][d] (a value column's d rows in a run).  out [rows][H * dv] 32-bit, rows >= the entries' tokens.
+// Entries of no tokens are left out.
 VCB_API int vcb_matrix_rnn(int mode, const float* u, int S, long long s_stride, long long ld, const float* x, long long ldx,
                            int q_col, int k_col, int v_col, int b_col, int a_col, const float* dt_bias, const float* rate,
                            const float* f_bias, const float* lower, float* state, long long state_stride, const int* q_start,
                            const int* q_len, const int* slots, int E, int rows, int H, int G, int d, int dv, float* out,
-                           cudaStream_t stream) {
+                           const float* z, int zS, long long z_stride, long long zld, float inv_tau, const float* decay,
+                           const int* ctx_len, const float* freq, int rot, int interleaved, cudaStream_t stream) {
     if (E == 0) return 0;
-    VCB_CHECK_ARG(mode == 0 || mode == 1, "matrix_rnn: unknown mode %d", mode);
+    VCB_CHECK_ARG(mode >= 0 && mode <= 3, "matrix_rnn: unknown mode %d", mode);
+    VCB_CHECK_ARG(mode != 2 || (z != nullptr && f_bias != nullptr), "matrix_rnn: the decayed form needs the decay's sums and bias");
+    VCB_CHECK_ARG(mode != 3 || (decay != nullptr && ctx_len != nullptr && rot >= 0 && rot <= d && rot % 2 == 0 && (rot == 0 || freq != nullptr)),
+                  "matrix_rnn: retention needs a decay per head, the entries' positions and %d <= %d turning lanes with their frequencies", rot, d);
     VCB_CHECK_ARG(d >= 1 && d <= 512, "matrix_rnn: %d state rows a head (1 to 512)", d);
     VCB_CHECK_ARG(H >= 1 && G >= 1 && H % G == 0 && dv >= 1, "matrix_rnn: bad sizes H=%d G=%d dv=%d", H, G, dv);
     VCB_CHECK_ARG(H <= 65535 && E <= 65535, "matrix_rnn: %d heads, %d entries", H, E);
@@ -519,14 +586,15 @@ VCB_API int vcb_matrix_rnn(int mode, const float* u, int S, long long s_stride, 
     while ((1 << dp_shift) < DP) ++dp_shift;
     while ((1 << ct_shift) < CT) ++ct_shift;
     RnnArgs a{Rows{u, S < 1 ? 1 : S, s_stride, ld}, x, ldx, q_col, k_col, v_col, b_col, a_col, dt_bias, rate, f_bias, lower, state,
-              state_stride, q_start, q_len, slots, out, H, G, d, dv, L, TB, dp_shift, ct_shift};
-    const size_t smem = (size_t)(2 * (2 * TB * DP + TB * CT + 2 * TB) + TB * CT) * sizeof(float);
+              state_stride, q_start, q_len, slots, out, H, G, d, dv, L, TB, dp_shift, ct_shift,
+              Rows{z, zS < 1 ? 1 : zS, z_stride, zld}, inv_tau, decay, ctx_len, freq, rot, interleaved};
+    const size_t smem = (size_t)(2 * ((mode == 2 ? 3 : 2) * TB * DP + TB * CT + 2 * TB) + TB * CT) * sizeof(float);
     const dim3 grid((dv + CT - 1) / CT, H, E);
     const bool split = rows > 4 * E;    // some entry has more than four tokens
     int rc;
 #define VCB_RNN_GO(MODE_, R_) (C == 1 ? rnn_launch<MODE_, R_, 1>(a, split, grid, smem, stream) : rnn_launch<MODE_, R_, 2>(a, split, grid, smem, stream))
-    if (R == 8) rc = mode == 0 ? VCB_RNN_GO(MODE_DELTA, 8) : VCB_RNN_GO(MODE_GATED, 8);
-    else rc = mode == 0 ? VCB_RNN_GO(MODE_DELTA, 16) : VCB_RNN_GO(MODE_GATED, 16);
+    if (R == 8) rc = mode == 0 ? VCB_RNN_GO(MODE_DELTA, 8) : mode == 1 ? VCB_RNN_GO(MODE_GATED, 8) : mode == 2 ? VCB_RNN_GO(MODE_DECAYED, 8) : VCB_RNN_GO(MODE_RETAIN, 8);
+    else rc = mode == 0 ? VCB_RNN_GO(MODE_DELTA, 16) : mode == 1 ? VCB_RNN_GO(MODE_GATED, 16) : mode == 2 ? VCB_RNN_GO(MODE_DECAYED, 16) : VCB_RNN_GO(MODE_RETAIN, 16);
 #undef VCB_RNN_GO
     if (rc != 0) return rc;
     VCB_CHECK_LAUNCH("matrix_rnn");

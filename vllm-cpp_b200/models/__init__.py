@@ -10,6 +10,7 @@ from . import qwen3  # registers Qwen3ForCausalLM
 from . import rimopel  # registers Rimopel
 from . import nagavik  # registers Nagavik
 from . import fifudra  # registers Fifudra
+from . import mefupel  # registers Mefupel
 from .decoder import DecoderModel
 
 

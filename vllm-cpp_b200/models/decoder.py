@@ -36,6 +36,9 @@ class DecoderModel:
             self.final_norm = part_class("norm", spec.final_norm.kind)(spec.final_norm.params, spec.final_norm_prefix, build)
         self.lm_head = part_class("head", head.kind)(head.params, "", build)
         self.lm_head.attach(self.embedding)
+        self.reentry = None
+        if spec.reentry is not None:
+            self.reentry = part_class("reentry", spec.reentry.kind)(spec.reentry.params, "", build)
         self.order = list(spec.order)
         self._handed = None     # (the per-id views last given to forward, the same by run)
         for run in self.order:
@@ -46,6 +49,7 @@ class DecoderModel:
     def capturable(self) -> bool:
         """Whether a decoding step of this model can be captured as a CUDA graph."""
         parts = [p for layer in self.layers for p in layer.parts.values()] + [self.embedding, self.lm_head]
+        parts += [self.reentry] if self.reentry is not None else []
         return all(getattr(p, "capturable", True) for p in parts)
 
     # ---- weights ----
@@ -55,6 +59,8 @@ class DecoderModel:
             specs += layer.tensor_specs()
         if self.final_norm is not None:
             specs += self.final_norm.tensor_specs()
+        if self.reentry is not None:
+            specs += self.reentry.tensor_specs()
         return specs + self.lm_head.tensor_specs()
 
     def load(self, store: WeightStore) -> None:
@@ -64,6 +70,8 @@ class DecoderModel:
             layer.bind(store)
         if self.final_norm is not None:
             self.final_norm.bind(store)
+        if self.reentry is not None:
+            self.reentry.bind(store)
         self.lm_head.bind(store)
 
     # ---- caches ----
@@ -108,10 +116,19 @@ class DecoderModel:
     def forward(self, ctx, caches):
         """ctx: the step's tensors; caches: cache id -> view.  Returns 32-bit logits [rows, vocab]."""
         mark = getattr(ctx, "mark", lambda label: None)     # kernel groups for the profile, where the step keeps one
-        if getattr(self.embedding, "uses_positions", False):
-            resid = self.embedding.forward(ctx.token_ids, ctx.T, ctx.status, positions=ctx.positions)
-        else:
-            resid = self.embedding.forward(ctx.token_ids, ctx.T, ctx.status)
+
+        def embed():
+            if getattr(self.embedding, "uses_positions", False):
+                return self.embedding.forward(ctx.token_ids, ctx.T, ctx.status, positions=ctx.positions)
+            return self.embedding.forward(ctx.token_ids, ctx.T, ctx.status)
+
+        resid = embed()
+        # a part that re-enters the embedding's rows later in the step gets them in a buffer of their own (the stream
+        # itself is updated in place): the same gather once more, into the region that lives as long as the step
+        first_rows = None
+        if self.reentry is not None and getattr(self.reentry, "needs_embedding", False):
+            with workspace.whole_step():
+                first_rows = embed()
         mark("embedding")
         pending = None
         if self._handed is None or self._handed[0] is not caches:
@@ -120,6 +137,8 @@ class DecoderModel:
         for i, run in enumerate(self.order):
             cache = caches[run.cache] if run.cache is not None else None
             workspace.begin_run(i)      # the run's buffers come from the scratch region that run i - 2 used
+            if run.opens is not None and self.reentry is not None:
+                pending = self.reentry.forward(resid, pending, first_rows, run.opens)
             pending = self.layers[run.layer].forward(resid, pending, ctx, cache, run.writes)
         workspace.end_runs()
         if ctx.n_rows == 0:

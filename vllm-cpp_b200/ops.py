@@ -69,7 +69,7 @@ def _declare(L):
         "vcb_sgemm_tn": [P, P, P, I, I, I, LL, LL, LL, P],
         "vcb_gemm_bf16_plain": [P, P, P, I, I, I, I, LL, LL, LL, P],
         "vcb_attn_paged": [P, P, I, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, P, P],
-        "vcb_attn_paged_ex": [P, P, I, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, I, P, P, I, F, P, I, P, P],
+        "vcb_attn_paged_ex": [P, P, I, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, I, P, P, I, F, P, I, P, P, P],
         "vcb_embed_sinusoid": [P, I, P, P, P, P, I, I, I, P, P],
         "vcb_causal_conv": [P, I, LL, LL, P, P, P, LL, P, P, P, I, I, I, I, I, P, P, I, P, I, P],
         "vcb_embed_scaled_pos": [P, I, P, P, P, I, F, P, I, I, I, I, P, P],
@@ -85,7 +85,13 @@ def _declare(L):
         "vcb_latent_norm_rope_store": [P, I, LL, LL, P, P, F, P, P, F, P, P, P, LL, I, I, I, I, I, I, I, I, P, P],
         "vcb_head_linear": [P, I, I, LL, LL, I, I, P, I, P, I, LL, I, I, I, I, I, I, P],
         "vcb_rope_rows": [P, I, LL, LL, I, I, P, P, F, P, I, LL, I, I, I, I, I, I, P],
-        "vcb_matrix_rnn": [I, P, I, LL, LL, P, LL, I, I, I, I, I, P, P, P, P, P, LL, P, P, P, I, I, I, I, I, I, P, P],
+        "vcb_matrix_rnn": [I, P, I, LL, LL, P, LL, I, I, I, I, I, P, P, P, P, P, LL, P, P, P, I, I, I, I, I, I, P,
+                           P, I, LL, LL, F, P, P, P, I, I, P],
+        "vcb_sum_add_rmsnorm": [P, I, P, P, P, P, P, P, P, F, P, I, P, I, I, P],
+        "vcb_branch_norm_mean": [I, P, P, P, P, P, F, P, I, I, P],
+        "vcb_polynorm": [P, I, LL, LL, P, F, P, I, I, I, P],
+        "vcb_qkv_rope_store": [P, I, LL, LL, P, P, F, P, P, P, P, P, P, LL, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
+        "vcb_rotate_heads": [P, I, P, P, F, I, I, I, I, I, P],
         "vcb_head_norm_gate": [P, P, I, LL, LL, I, P, F, P, P, I, I, I, I, P, I, P],
         "vcb_moe_route_grouped": [P, I, LL, LL, P, I, I, F, P, P, I, I, I, I, P, P, P],
         "vcb_moe_group": [P, I, I, I, I, P, P, P, P],
@@ -421,8 +427,12 @@ def attn_window_bias(q, out, pages, block_table, q_start, q_len, ctx_len, items,
     a request stay visible; ``dist_a``/``dist_b`` (float32 [nh]): a_h ln(1 + b_h (pos - j)) is taken off key j's
     score; values of head size ``hd_v`` (``pages`` then [num_pages, nkv * page_size * (hd + hd_v)]); ``softcap`` c > 0:
     the scaled score becomes c tanh(s / c); ``slope`` (float32 [nh]): slope_h (pos - j) is taken off after the cap;
-    ``sink``: a silent key of score 0 and no value takes part in every softmax."""
+    ``sink``: a silent key of score 0 and no value takes part in every softmax; given as a float32 tensor [nh], the
+    silent key's score per head (not scaled)."""
     hd_v = hd if hd_v is None else int(hd_v)
+    sink_value = sink if torch.is_tensor(sink) else None
+    if sink_value is not None:
+        _need(sink_value, "sink", torch.float32); assert sink_value.numel() == nh
     _need(q, "q"); _need(out, "out", q.dtype); _need(pages, "pages", q.dtype)
     for name, t in (("block_table", block_table), ("q_start", q_start), ("q_len", q_len), ("ctx_len", ctx_len),
                     ("items", items)):
@@ -437,7 +447,7 @@ def attn_window_bias(q, out, pages, block_table, q_start, q_len, ctx_len, items,
     _call("vcb_attn_paged_ex", _p(q), _p(out), _dt(q), _p(pages), pages.stride(0), _p(block_table), _p(table_row),
           block_table.shape[1], _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items, rows_max, _p(part_o), _p(part_ml),
           nh, nkv, hd, page_size, num_pages, int(window or 0), float(scale), int(keep_first or 0), _p(dist_a), _p(dist_b),
-          hd_v, float(softcap or 0.0), _p(slope), int(bool(sink)), _p(status), _stream())
+          hd_v, float(softcap or 0.0), _p(slope), int(sink_value is not None or bool(sink)), _p(sink_value), _p(status), _stream())
 
 
 def embed_sinusoid(table, ids, positions, inv_freq, out, status):
@@ -549,16 +559,18 @@ def gated_norm_add(resid, y, gate, gate_bias, weight, eps, q_start, q_len, n_ent
 
 
 ACTIVATIONS = {"gelu": 0, "gelu_erf": 0, "gelu_tanh": 1, "silu": 2, "relu2": 3}
+ELEMENTWISE = dict(ACTIVATIONS, identity=4)    # what bias_act takes: the activations, and the sums as they are
 
 
 def bias_act(x, out, kind: str, bias=None):
-    """out = act(x + bias): x 32-bit [T, C] or [S, T, C] partial sums; ``kind`` one of ACTIVATIONS."""
+    """out = act(x + bias): x 32-bit [T, C] or [S, T, C] partial sums; ``kind`` one of ACTIVATIONS, or "identity" (the
+    sums themselves, added up and in ``out``'s type)."""
     S, ss, ld = _rows_in(x, "x")
     T, C = x.shape[-2:]
     _need(out, "out"); assert out.shape == (T, C)
-    if kind not in ACTIVATIONS:
-        raise KernelError(f"activation '{kind}' is not one of {sorted(ACTIVATIONS)}")
-    _call("vcb_bias_act", _p(x), S, ss, ld, _p(bias), _p(out), _dt(out), T, C, ACTIVATIONS[kind], _stream())
+    if kind not in ELEMENTWISE:
+        raise KernelError(f"activation '{kind}' is not one of {sorted(ELEMENTWISE)}")
+    _call("vcb_bias_act", _p(x), S, ss, ld, _p(bias), _p(out), _dt(out), T, C, ELEMENTWISE[kind], _stream())
 
 
 def embed_scaled_pos(table, ids, positions, pos_table, scale, out, status):
@@ -1131,38 +1143,58 @@ def rope_rows(x, positions, freq, gain, out, *, heads, dims, width, in_head_stri
 
 
 def matrix_rnn(mode, u, state, q_start, q_len, slots, n_entries, out, *, heads, d, dv, q_col, k_col, v_col, x=None,
-               kv_heads=None, b_col=0, a_col=0, dt_bias=None, rate=None, f_bias=None, lower=None):
+               kv_heads=None, b_col=0, a_col=0, dt_bias=None, rate=None, f_bias=None, lower=None, z=None, tau=1.0, decay=None,
+               ctx_len=None, freq=None, rot=0, interleaved=False):
     """A recurrence over each entry's tokens whose state S [d, dv] per head lies in ``state`` [slots, heads, dv, d] (32-bit, a value column's rows in a run), ``out`` [T, heads dv].
 
     ``mode`` "delta": S <- g S; w = beta (v - S^T k); S <- S + k w^T; o = S^T q.  q, k, v are columns ``q_col``,
     ``k_col``, ``v_col`` of ``x`` [T, C] (32-bit, convolved and activated; q and k of ``kv_heads`` heads, made unit
     vectors here, q times d^(-1/2)); beta = sigmoid(u[:, b_col + h]), g = exp(-rate_h softplus(u[:, a_col + h] + dt_bias_h)).
     ``mode`` "gated": S <- diag(f) S + (1 - f) v^T; o = S^T q with q = silu(u[:, q_col ...]), f = lower + (1 - lower)
-    sigmoid(u[:, k_col ...] + f_bias), v = u[:, v_col ...].  ``u``: the projection's 32-bit sums ([S, T, C] partials)."""
+    sigmoid(u[:, k_col ...] + f_bias), v = u[:, v_col ...].
+    ``mode`` "decayed": S <- diag(f) S + k v^T; o = S^T q with q = u[:, q_col ...] d^(-1/2), k = u[:, k_col ...],
+    v = u[:, v_col ...] and f = sigmoid(z + f_bias)^(1 / tau), ``z`` [T, heads d] the 32-bit sums of a projection of its own.
+    ``mode`` "retention": S <- decay_h S + k v^T; o = S^T q with q, k, v columns of u, the first ``rot`` lanes of every q
+    and k head turned by position * freq[i] (lanes paired in halves, or ``interleaved``), k then times d^(-1/2);
+    positions from ``ctx_len``.
+    ``u``: the projection's 32-bit sums ([S, T, C] partials)."""
     S, ss, ld = _rows_in(u, "u")
     _need(state, "state", torch.float32, contiguous=False); _need(out, "out", torch.float32)
     assert state.shape[1:] == (heads, dv, d) and state[0].is_contiguous() and out.shape[1] == heads * dv
-    m = {"delta": 0, "gated": 1}[mode]
+    m = {"delta": 0, "gated": 1, "decayed": 2, "retention": 3}[mode]
     ldx = 0
+    zS = zss = zld = 0
     if m == 0:
         _need(x, "x", torch.float32, contiguous=False); assert x.stride(1) == 1
         ldx = x.stride(0)
         for name, t in (("dt_bias", dt_bias), ("rate", rate)):
             _need(t, name, torch.float32); assert t.numel() == heads
-    else:
+    elif m == 1:
         for name, t in (("f_bias", f_bias), ("lower", lower)):
             _need(t, name, torch.float32); assert t.numel() == heads * d
+    elif m == 2:
+        zS, zss, zld = _rows_in(z, "z")
+        _need(f_bias, "f_bias", torch.float32); assert f_bias.numel() == heads * d and z.shape[-1] == heads * d
+        assert z.shape[-2] >= out.shape[0] and tau > 0
+    else:
+        _need(decay, "decay", torch.float32); assert decay.numel() == heads
+        _need(ctx_len, "ctx_len", torch.int32)
+        if rot:
+            _need(freq, "freq", torch.float32); assert freq.numel() == rot // 2
     _call("vcb_matrix_rnn", m, _p(u), S, ss, ld, _p(x), ldx, int(q_col), int(k_col), int(v_col), int(b_col), int(a_col),
           _p(dt_bias), _p(rate), _p(f_bias), _p(lower), _p(state), state.stride(0), _p(q_start), _p(q_len), _p(slots),
-          n_entries, int(out.shape[0]), int(heads), int(kv_heads or heads), int(d), int(dv), _p(out), _stream())
+          n_entries, int(out.shape[0]), int(heads), int(kv_heads or heads), int(d), int(dv), _p(out),
+          _p(z), zS, zss, zld, 1.0 / float(tau), _p(decay), _p(ctx_len), _p(freq), int(rot), int(bool(interleaved)), _stream())
 
 
 def head_norm_gate(o, weight, eps, q_start, q_len, n_entries, heads, dv, out, gate=None, gate_col=0):
     """out[t, h] = weight * o[t, h] / sqrt(mean(o[t, h]^2) + eps) (* silu(gate[t, gate_col + h dv ...]) with a gate):
-    every head of the 32-bit ``o`` [T, heads dv] by its own root mean square, one gain [dv] for all heads."""
-    _need(o, "o", torch.float32); _need(weight, "weight", torch.float32); _need(out, "out")
+    every head of the 32-bit ``o`` [T, heads dv] by its own root mean square, one gain [dv] for all heads (None: no gain)."""
+    _need(o, "o", torch.float32); _need(out, "out")
     T = o.shape[0]
-    assert o.shape == (T, heads * dv) and out.shape == o.shape and weight.numel() == dv
+    assert o.shape == (T, heads * dv) and out.shape == o.shape
+    if weight is not None:
+        _need(weight, "weight", torch.float32); assert weight.numel() == dv
     S = ss = ld = 0
     if gate is not None:
         S, ss, ld = _rows_in(gate, "gate")
@@ -1183,3 +1215,105 @@ def moe_route_grouped(logits, correction, n_groups, keep, weight_scale, q_start,
     assert sel_e.numel() == T * top and sel_w.numel() == T * top
     _call("vcb_moe_route_grouped", _p(logits), S, ss, ld, _p(correction), int(n_groups or 1), int(keep or 0), float(weight_scale),
           _p(q_start), _p(q_len), n_entries, T, E, int(top), _p(sel_e), _p(sel_w), _stream())
+
+
+# -------------------------------------------------------------------------- sublayers side by side on one normed input
+
+
+def _terms(tensors, name):
+    """A list of 32-bit [T, C] or [S, T, C] operands -> the four ctypes arrays a kernel that adds them all reads."""
+    n = len(tensors)
+    ptrs, counts, sstr, lds = (c_void_p * n)(), (c_int * n)(), (c_longlong * n)(), (c_longlong * n)()
+    for k, t in enumerate(tensors):
+        S, ss, ld = _rows_in(t, name)
+        ptrs[k], counts[k], sstr[k], lds[k] = t.data_ptr(), S, ss, ld
+    return ptrs, counts, sstr, lds
+
+
+def sum_add_rmsnorm(resid, terms, gain, eps, out, rows=None, row_extra=None, vec_extra=None):
+    """resid[t] += sum of ``terms`` (up to four 32-bit results, each [T, H] or [S, T, H] partial sums) + row_extra[t] +
+    vec_extra, then out = gain * resid[t] / sqrt(mean(resid[t]^2) + eps), in one pass.  ``gain`` 32-bit [H]; ``out`` None:
+    the additions alone.  With ``rows`` (int32 indices) only those rows are made and the stream is left alone."""
+    _need(resid, "resid", torch.float32)
+    T, H = resid.shape
+    terms = [t for t in terms if t is not None]
+    for t in terms:
+        assert t.shape[-1] == H and t.shape[-2] >= T, (t.shape, resid.shape)
+    for name, t, numel in (("row_extra", row_extra, None), ("vec_extra", vec_extra, H), ("gain", gain, H)):
+        if t is not None:
+            _need(t, name, torch.float32)
+            assert numel is None or t.numel() == numel
+    if row_extra is not None:
+        assert row_extra.shape[-1] == H and row_extra.shape[0] >= T
+    n = T if rows is None else rows.numel()
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    if out is not None:
+        _need(out, "out"); assert out.shape[0] >= n and out.shape[1] == H and gain is not None
+    ptrs, counts, sstr, lds = _terms(terms, "term")
+    _call("vcb_sum_add_rmsnorm", _p(resid), len(terms), ptrs, counts, sstr, lds, _p(row_extra), _p(vec_extra), _p(gain), float(eps),
+          _p(out), _dt(out) if out is not None else F32, _p(rows), n, H, _stream())
+
+
+def branch_norm_mean(results, gains, eps, out):
+    """out[t] = 1/N sum_b gains[b] * results[b][t] / sqrt(mean(results[b][t]^2) + eps): N results (32-bit [T, H] or
+    [S, T, H] partial sums) of mixers that read one input, each normed over the width with its own gain, averaged."""
+    _need(out, "out", torch.float32)
+    T, H = out.shape
+    assert len(results) == len(gains) and 1 <= len(results) <= 4
+    for g in gains:
+        _need(g, "gain", torch.float32); assert g.numel() == H
+    for r in results:
+        assert r.shape[-1] == H and r.shape[-2] >= T
+    ptrs, counts, sstr, lds = _terms(results, "result")
+    gp = (c_void_p * len(gains))(*[g.data_ptr() for g in gains])
+    _call("vcb_branch_norm_mean", len(results), ptrs, counts, sstr, lds, gp, float(eps), _p(out), T, H, _stream())
+
+
+def polynorm(u, coef, eps, out):
+    """out[t] = a n(z) + b n(z^2) + c n(z^3) + e with z = u[t] (32-bit sums [T, F] or [S, T, F]), powers lane by lane,
+    n(v) = v / sqrt(mean(v^2) + eps) over the F lanes, and (a, b, c, e) = ``coef`` (float32 [4] on the device)."""
+    S, ss, ld = _rows_in(u, "u")
+    T, Fw = u.shape[-2:]
+    _need(coef, "coef", torch.float32); _need(out, "out")
+    assert coef.numel() == 4 and out.shape == (T, Fw)
+    _call("vcb_polynorm", _p(u), S, ss, ld, _p(coef), float(eps), _p(out), _dt(out), T, Fw, _stream())
+
+
+# -------------------------------------------------------------------------- rotary attention with its options as parameters
+
+
+def qkv_rope_store(qkv, q_gain, k_gain, eps, positions, freq, vfreq, slot_map, q_out, pages, nh, nkv, hd, vd, status, *,
+                   rot, interleaved=False, values_from_keys=False):
+    """From the stacked projection's 32-bit sums ``qkv`` ([T, C] or [S, T, C]; C = nh hd + nkv hd + nkv vd, or without the
+    value columns where ``values_from_keys``: the keys as projected are the values): with ``q_gain`` [nh hd] / ``k_gain``
+    [nkv hd] all of a token's query (key) lanes divided by their root mean square times the gain; the first ``rot`` lanes
+    of every q and k head turned by position * freq[i], pairs (i, i + rot/2) or ``interleaved`` (2i, 2i+1); with
+    ``vfreq`` [vd/2] every value head turned likewise over all its lanes; queries to ``q_out``, keys and values to the
+    tokens' slots of ``pages`` (see :func:`kv_page_views`)."""
+    S, ss, ld = _rows_in(qkv, "qkv")
+    T, C = qkv.shape[-2:]
+    assert C == nh * hd + nkv * hd + (0 if values_from_keys else nkv * vd), (C, nh, nkv, hd, vd)
+    if q_gain is not None:
+        _need(q_gain, "q_gain", torch.float32); _need(k_gain, "k_gain", torch.float32)
+        assert q_gain.numel() == nh * hd and k_gain.numel() == nkv * hd
+    _need(positions, "positions", torch.int32); _need(slot_map, "slot_map", torch.int32)
+    if rot:
+        _need(freq, "freq", torch.float32); assert freq.numel() == rot // 2
+    if vfreq is not None:
+        _need(vfreq, "vfreq", torch.float32); assert vfreq.numel() == vd // 2 and vd % 2 == 0
+    _need(q_out, "q_out"); assert q_out.shape == (T, nh * hd)
+    _need(pages, "pages", q_out.dtype)
+    page_size, num_pages = kv_page_views(pages, nkv, hd, vd)
+    _call("vcb_qkv_rope_store", _p(qkv), S, ss, ld, _p(q_gain), _p(k_gain), float(eps), _p(positions), _p(freq), _p(vfreq),
+          _p(slot_map), _p(q_out), _p(pages), pages.stride(0), page_size, num_pages, nh, nkv, hd, vd, int(rot), vd,
+          int(bool(interleaved)), int(bool(values_from_keys)), T, _dt(q_out), _p(status), _stream())
+
+
+def rotate_heads(x, positions, freq, *, heads, width, dims, interleaved=False, sign=1.0):
+    """x [T, heads * width] in place: the first ``dims`` lanes of every head turned by sign * position * freq[i]."""
+    _need(x, "x"); _need(positions, "positions", torch.int32); _need(freq, "freq", torch.float32)
+    T = x.shape[0]
+    assert x.shape[1] == heads * width and freq.numel() == dims // 2
+    _call("vcb_rotate_heads", _p(x), _dt(x), _p(positions), _p(freq), float(sign), T, int(heads), int(width), int(dims),
+          int(bool(interleaved)), _stream())

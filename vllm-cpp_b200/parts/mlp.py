@@ -60,19 +60,25 @@ class SwiGLUMLP(FeedForward):
 
 class DenseMLP(FeedForward):
     """down(act(up(y))): one hidden layer, act the exact (erf) GELU unless ``activation`` names another
-    ("gelu_erf", "gelu_tanh": 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), "silu").  The hidden layer's sums and
-    the activation are 32-bit; what the down projection reads is in the compute dtype.
+    ("gelu_erf", "gelu_tanh": 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), "silu", or "polynorm": a n(z) + b n(z^2)
+    + c n(z^3) + e with powers lane by lane, n(v) = v / sqrt(mean(v^2) + eps) over a token's hidden lanes and the four
+    learned numbers a, b, c, e).  The hidden layer's sums and the activation are 32-bit; what the down projection reads
+    is in the compute dtype.
 
     params: ``hidden_size``, ``intermediate_size``; optional ``activation``, ``up_tensor`` and ``down_tensor``
-    (names under the prefix, default "up_proj.weight" and "down_proj.weight")."""
+    (names under the prefix, default "up_proj.weight" and "down_proj.weight"); with "polynorm" also ``act_tensor``
+    (default "act", a tensor [4]) and ``eps``."""
 
     def __init__(self, params, prefix, build):
         super().__init__(params, prefix, build)
         self.hidden = int(params["hidden_size"])
         self.inter = int(params["intermediate_size"])
         self.activation = str(params.get("activation", "gelu_erf"))
-        if self.activation not in ops.ACTIVATIONS:
-            raise ValueError(f"activation '{self.activation}' is not one of {sorted(ops.ACTIVATIONS)}")
+        if self.activation not in ops.ACTIVATIONS and self.activation != "polynorm":
+            raise ValueError(f"activation '{self.activation}' is not one of {sorted(ops.ACTIVATIONS) + ['polynorm']}")
+        self.act_name = prefix + str(params.get("act_tensor", "act"))
+        self.eps = float(params.get("eps", 1e-6))
+        self.coef = None
         self.up_name = prefix + str(params.get("up_tensor", "up_proj.weight"))
         self.down_name = prefix + str(params.get("down_tensor", "down_proj.weight"))
         self.w_up = self.w_down = None
@@ -80,11 +86,16 @@ class DenseMLP(FeedForward):
         self.side = None
 
     def tensor_specs(self):
-        return [TensorSpec(self.up_name, (self.inter, self.hidden)), TensorSpec(self.down_name, (self.hidden, self.inter))]
+        specs = [TensorSpec(self.up_name, (self.inter, self.hidden)), TensorSpec(self.down_name, (self.hidden, self.inter))]
+        if self.activation == "polynorm":
+            specs.append(TensorSpec(self.act_name, (4,), "vector"))
+        return specs
 
     def bind(self, store):
         self.w_up = store.matrix(self.up_name)
         self.w_down = store.matrix(self.down_name)
+        if self.activation == "polynorm":
+            self.coef = store.vector(self.act_name).float().contiguous()
 
     def attach_side_rows(self, weight) -> None:
         """Stacks ``weight`` [rows, hidden] under the up projection (after ``bind``): whoever else multiplies the part's
@@ -99,7 +110,10 @@ class DenseMLP(FeedForward):
             self.side = u[..., self.inter:]
             u = u[..., :self.inter]
         act = workspace.empty((x.shape[0], self.inter), x.dtype, x.device)
-        ops.bias_act(u, act, self.activation)
+        if self.activation == "polynorm":
+            ops.polynorm(u, self.coef, self.eps, act)
+        else:
+            ops.bias_act(u, act, self.activation)
         return matmul_tn(act, self.w_down, ctx.status, out_dtype=torch.float32, allow_partials=True, after_small_kernel=True)
 
 

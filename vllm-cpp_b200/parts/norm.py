@@ -11,21 +11,26 @@ from .base import Norm
 
 
 class RMSNorm(Norm):
-    """params: ``size``, ``eps``; optional ``name`` (default "weight").  Tensor: ``<prefix><name>`` [size]."""
+    """params: ``size``, ``eps``; optional ``name`` (default "weight"); ``one_plus`` (default False): the tensor holds the
+    gain less one (values around zero), y = (1 + w) * x / sqrt(mean(x^2) + eps), the sum made in 32-bit.
+    Tensor: ``<prefix><name>`` [size]."""
 
     def __init__(self, params, prefix, build):
         super().__init__(params, prefix, build)
         self.size = int(params["size"])
         self.eps = float(params["eps"])
         self.name = self.prefix + str(params.get("name", "weight"))
+        self.one_plus = bool(params.get("one_plus", False))
         self.weight = None
         self._gain32 = None
 
     def tensor_specs(self):
-        return [TensorSpec(self.name, (self.size,), "vector")]
+        return [TensorSpec(self.name, (self.size,), "bias" if self.one_plus else "vector")]
 
     def bind(self, store):
         self.weight = store.vector(self.name)
+        if self.one_plus:
+            self.weight = (1.0 + self.weight.float()).contiguous()
 
     def gain32(self):
         """The gain as a 32-bit vector (made once): what the kernels that fuse this norm with other steps read."""

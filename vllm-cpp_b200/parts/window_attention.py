@@ -43,11 +43,14 @@ from .linear import matmul_tn
 MMA_ATTENTION = os.environ.get("VLLM_CPP_B200_WINDOW_ATTN_MMA", "1") != "0"
 # whether the tensor-core kernels take the cap, the slope and the sink (else steps with them run on the plain kernel)
 EXTRAS_ON_TENSOR_CORES = True
+# whether they take a sink with a learned score per head (else such steps run on the plain kernel)
+SINK_SCORES_ON_TENSOR_CORES = False
 
 
 def paged_attention(ctx, kv, q, out, *, nh, nkv, hd, vd, scale, window=0, keep_first=0, dist_a=None, dist_b=None,
                     softcap=0.0, slope=None, sink=False):
-    """Scores, softmax and weighted sums of one step over the paged keys and values ``kv``: ``q`` [T, nh * hd] against
+    """(``sink``: False, True -- a silent key of score 0 --, or a float32 tensor [nh] of the silent key's score per head.)
+    Scores, softmax and weighted sums of one step over the paged keys and values ``kv``: ``q`` [T, nh * hd] against
     keys of ``hd`` lanes, values of ``vd`` lanes into ``out`` [T, nh * vd].  Single tokens are cut into key slices and
     merged, prompt portions into row tiles; bfloat16 with keys and values of 64 or 128 lanes runs on the tensor cores
     (tcgen05 for prompt portions where the page size allows, mma.sync for decoded tokens), everything else on the
@@ -58,9 +61,10 @@ def paged_attention(ctx, kv, q, out, *, nh, nkv, hd, vd, scale, window=0, keep_f
     reach = window + keep_first if window else 0
     # bfloat16 with keys and values of 64 or 128 lanes: the tensor-core kernel; else the plain one
     extras = dict(softcap=softcap, slope=slope, sink=sink)
-    has_extras = bool(softcap or slope is not None or sink)
+    learned_sink = torch.is_tensor(sink)
+    has_extras = bool(softcap or slope is not None or learned_sink or sink)
     mma = (MMA_ATTENTION and vd == hd and kv.pages.dim() == 5 and ops.attn_mma_supported(x.dtype, hd)
-           and (EXTRAS_ON_TENSOR_CORES or not has_extras))
+           and (EXTRAS_ON_TENSOR_CORES or not has_extras) and (SINK_SCORES_ON_TENSOR_CORES or not learned_sink))
     dec_rows, span_rows = (MMA_DECODE_ROWS, MMA_SPAN_ROWS) if mma else (DECODE_ROWS, SPAN_ROWS)
     clustered = hd if mma and CLUSTER_MERGE and torch.cuda.is_available() else None
     group = ctx.groups[kv.group]
@@ -197,3 +201,115 @@ class ConvWindowAttention(Mixer):
                         keep_first=self.keep_first, dist_a=self.dist_a, dist_b=self.dist_b, softcap=self.softcap,
                         slope=self.slope, sink=self.sink)
         return matmul_tn(out, self.w_o, ctx.status, out_dtype=torch.float32, allow_partials=True)
+
+
+def rotary_frequencies(build, base: float, dims: int) -> torch.Tensor:
+    """base^(-2i / dims), i < dims / 2: 64-bit on the host, rounded once to 32-bit, shared by parts with equal numbers."""
+    key = ("rotary_freq", float(base), int(dims))
+    if key not in build.shared:
+        i = torch.arange(dims // 2, dtype=torch.float64)
+        build.shared[key] = (float(base) ** (-2.0 * i / dims)).to(torch.float32).to(build.device)
+    return build.shared[key]
+
+
+class RotaryWindowAttention(Mixer):
+    """Grouped-query softmax attention with rotary positions, every variation a parameter:
+
+        q, k, v = W_q x, W_k x, W_v x                 (one stacked product; no biases)
+        ``values_from_keys``: there is no W_v; v = k as projected, before any norm or rotation (v_head_dim = head_dim)
+        ``whole_norm``:       q <- g_q * q / rms(q) over all of a token's query lanes at once, k likewise with g_k
+        the first ``rotary_dim`` lanes of every q and k head turn by position * base^(-2i / rotary_dim), lanes paired
+        in halves (i, i + rotary_dim/2; ``pairing`` "half") or as neighbours (2i, 2i+1; "interleaved")
+        ``rotate_values``:    the value of position j turns by j over all its lanes (same pairing, frequencies
+                              base^(-2m / v_head_dim)) and is cached so; a head's weighted sum at position i is turned
+                              back by i, which leaves every value turned by j - i
+        s_ij = scale * (q_i . k_j);  i sees j iff 0 <= i - j < window (window 0: every j <= i)
+        ``sink``:             exp(sink_h), a learned score per head that is not scaled, joins the softmax's denominator
+        softmax, weighted sum of the values, output projection.
+
+    params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``v_head_dim`` (default head_dim), ``scale``,
+    ``window``, ``rope_base``, ``rotary_dim``, ``pairing``, ``eps`` and the flags above (all default False).
+    Tensors under ``<prefix>``: q [nh hd, H], k [nkv hd, H], v [nkv vd, H] (unless values_from_keys), o [H, nh vd];
+    q.norm [nh hd], k.norm [nkv hd] (whole_norm); sink [nh] (sink).
+
+    Norms, angles, scores and softmax are 32-bit; queries, keys and values are stored in the compute dtype.  Keys and
+    values lie in pages that are given back as the window passes."""
+
+    def __init__(self, params, prefix, build):
+        super().__init__(params, prefix, build)
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.nh, self.nkv, self.hd = int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"])
+        self.vd = int(p.get("v_head_dim") or self.hd)
+        self.scale = float(p["scale"]) if p.get("scale") is not None else self.hd ** -0.5
+        self.window = int(p.get("window") or 0)
+        self.eps = float(p.get("eps", 1e-6))
+        self.rot = int(p.get("rotary_dim") if p.get("rotary_dim") is not None else self.hd)
+        self.interleaved = str(p.get("pairing") or "half") == "interleaved"
+        if str(p.get("pairing") or "half") not in ("half", "interleaved"):
+            raise ValueError(f"rotary pairing '{p.get('pairing')}' is not one of 'half', 'interleaved'")
+        self.values_from_keys = bool(p.get("values_from_keys", False))
+        self.whole_norm = bool(p.get("whole_norm", False))
+        self.rotate_values = bool(p.get("rotate_values", False))
+        self.has_sink = bool(p.get("sink", False))
+        if self.nh % self.nkv:
+            raise ValueError(f"{self.nh} query heads are not a multiple of {self.nkv} KV heads")
+        if self.values_from_keys and self.vd != self.hd:
+            raise ValueError("keys that double as values have the keys' size")
+        if self.rot % 2 or not 0 <= self.rot <= self.hd:
+            raise ValueError(f"{self.rot} turning lanes in heads of {self.hd}: an even number up to the head size")
+        if self.rotate_values and self.vd % 2:
+            raise ValueError(f"values of {self.vd} lanes cannot turn in pairs")
+        for n in (self.hd, self.vd):
+            if not 1 <= n <= 256:
+                raise ValueError(f"head size {n} is not supported: the kernels take 1 to 256")
+        base = float(p.get("rope_base", 10000.0))
+        self.freq = rotary_frequencies(build, base, self.rot) if self.rot else None
+        self.vfreq = rotary_frequencies(build, base, self.vd) if self.rotate_values else None
+        self.w_qkv = self.w_o = self.q_gain = self.k_gain = self.sink = None
+
+    def cache_spec(self):
+        return CacheSpec("kv", num_kv_heads=self.nkv, head_dim=self.hd, window=self.window,
+                         v_head_dim=0 if self.vd == self.hd else self.vd)
+
+    def _rows(self):
+        rows = [("q", self.nh * self.hd), ("k", self.nkv * self.hd)]
+        return rows if self.values_from_keys else rows + [("v", self.nkv * self.vd)]
+
+    def tensor_specs(self):
+        p, H = self.prefix, self.hidden
+        specs = [TensorSpec(p + n, (r, H)) for n, r in self._rows()] + [TensorSpec(p + "o", (H, self.nh * self.vd))]
+        if self.whole_norm:
+            specs += [TensorSpec(p + "q.norm", (self.nh * self.hd,), "vector"), TensorSpec(p + "k.norm", (self.nkv * self.hd,), "vector")]
+        if self.has_sink:
+            specs.append(TensorSpec(p + "sink", (self.nh,), "bias"))
+        return specs
+
+    def bind(self, store):
+        p = self.prefix
+        f32 = lambda name: store.vector(p + name).float().contiguous()
+        self.w_qkv = store.matrices([p + n for n, _ in self._rows()])
+        self.w_o = store.matrix(p + "o")
+        if self.whole_norm:
+            self.q_gain, self.k_gain = f32("q.norm"), f32("k.norm")
+        if self.has_sink:
+            self.sink = f32("sink")
+
+    def forward(self, x, ctx, cache, writes=True):
+        if not writes:
+            raise ValueError("this attention part keeps its own keys: it cannot read a cache another run filled")
+        kv = cache
+        T = x.shape[0]
+        nh, nkv, hd, vd = self.nh, self.nkv, self.hd, self.vd
+        group = ctx.groups[kv.group]
+        qkv = matmul_tn(x, self.w_qkv, ctx.status, out_dtype=torch.float32, allow_partials=True, after_small_kernel=True)
+        q = workspace.empty((T, nh * hd), x.dtype, x.device)
+        ops.qkv_rope_store(qkv, self.q_gain, self.k_gain, self.eps, ctx.positions, self.freq, self.vfreq, group.slot_map, q,
+                           kv.pages, nh, nkv, hd, vd, ctx.status, rot=self.rot, interleaved=self.interleaved,
+                           values_from_keys=self.values_from_keys)
+        out = workspace.empty((T, nh * vd), x.dtype, x.device)
+        paged_attention(ctx, kv, q, out, nh=nh, nkv=nkv, hd=hd, vd=vd, scale=self.scale, window=self.window,
+                        sink=self.sink if self.has_sink else False)
+        if self.rotate_values:
+            ops.rotate_heads(out, ctx.positions, self.vfreq, heads=nh, width=vd, dims=vd, interleaved=self.interleaved, sign=-1.0)
+        return matmul_tn(out, self.w_o, ctx.status, out_dtype=torch.float32, allow_partials=True, after_small_kernel=True)

@@ -16,7 +16,7 @@ from typing import Any, Callable
 
 from .config.base import ConfigError, ModelConfig
 
-PART_FAMILIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
+PART_FAMILIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head", "reentry")
 # the family of a layer's part when its LayerSpec names none: by the role it plays in the block
 ROLE_FAMILIES = {"norm1": "norm", "norm2": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
 
@@ -62,10 +62,13 @@ class LayerRun:
 
     ``writes`` False makes the mixer read a cache that an earlier run filled
     (it must then need no keys of its own).  A layer may appear in several
-    runs, each with a cache of its own."""
+    runs, each with a cache of its own.  ``opens`` t: this run is the first of pass t
+    over a repeated stretch of layers; the model's ``reentry`` part says what the
+    stream receives before it."""
     layer: int
     cache: int | None
     writes: bool = True
+    opens: int | None = None
 
 
 @dataclass(frozen=True)
@@ -73,7 +76,8 @@ class ModelSpec:
     """What a model is made of.  The embedding and the head are parts like the rest: ``embedding`` and ``head`` name
     them (families "embedding" and "head"); left out, they are the plain token embedding over ``embed_tensor`` and
     the plain LM head over ``lm_head_tensor`` (None: tied to the embedding table).  ``final_norm`` None: the head
-    reads the residual stream as it is."""
+    reads the residual stream as it is.  ``reentry`` (family "reentry"): what is added to the stream before the runs
+    that open a pass (``LayerRun.opens``); None: nothing."""
     hidden_size: int
     vocab_size: int
     max_positions: int
@@ -86,6 +90,7 @@ class ModelSpec:
     stop_ids: tuple = ()
     embedding: PartSpec | None = None
     head: PartSpec | None = None
+    reentry: PartSpec | None = None
 
     def embedding_spec(self) -> PartSpec:
         return self.embedding or PartSpec("token_embedding", {"tensor": self.embed_tensor, "vocab_size": self.vocab_size,

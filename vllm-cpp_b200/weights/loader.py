@@ -28,7 +28,7 @@ class WeightError(ValueError):
 @dataclass(frozen=True)
 class TensorSpec:
     name: str
-    shape: tuple
+    shape: tuple             # an entry of -1: any size there (a size that only the checkpoint knows; its part checks it)
     # "matrix" (operand of a matrix product), "vector" (gains), "bias" (additive terms, convolution taps), "positive"
     # (rates that must not be negative), "unit" (numbers in [0, 1)), "mixing" (a small square matrix near the identity),
     # "table" (integers); all but the first and last are read with ``vector``
@@ -58,7 +58,8 @@ class WeightStore:
         unexpected = sorted(n for n in self._tensors if n not in expected)
         wrong = []
         for n, s in expected.items():
-            if n in self._tensors and tuple(self._tensors[n].shape) != tuple(s.shape):
+            found = tuple(self._tensors[n].shape) if n in self._tensors else ()
+            if n in self._tensors and (len(found) != len(s.shape) or any(w >= 0 and w != f for w, f in zip(s.shape, found))):
                 wrong.append(f"{n}: expected {tuple(s.shape)}, found {tuple(self._tensors[n].shape)}")
         if missing or unexpected or wrong:
             def show(items):
