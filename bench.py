@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Benchmark of the engine on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--workloads all|headline|14b|4b|rimopel|nagavik|fifudra] [--impl reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--workloads all|headline|14b|4b|rimopel|nagavik|fifudra|mefupel] [--impl reference]
 
 Headline: decode tokens/s of the Qwen3-8B layer sizes (the baseline's third configuration) at batch 8 and context
 4,096, the median of K device-timed steps after W warm-up steps; beside it batch 1 and 64, batch 8 at context 2,176
@@ -710,6 +710,95 @@ def run_fifudra(args, pk, clocks, windows):
     return run_beside(args, pk, clocks, windows, "fifudra_beside_nagavik", FIFUDRA_SIZES, configs, numbers)
 
 
+# Mefupel at real layer sizes beside Fifudra, the closest design the engine has (recurrences on a matrix state per head
+# between attention layers, a stretch of layers that runs twice), at equal width, layer count, repeated stretch,
+# recurrent state per request and feed-forward parameters: a gated-linear-attention layer, a layer of window attention
+# beside retention, a window attention layer with turned values, and so on, each with a dense feed-forward of two
+# matrices; Fifudra with its dense gated feed-forward of three.
+MEFUPEL_SIZES = {
+    "w2048": dict(width=2048, layers=12, loop=(3, 6, 2), vocab=32768, heads=16, kv_heads=4, dim=128, window=1024, rot=64,
+                  r_heads=16, r_dim=128, r_vdim=256, rank=64, ff=6144,
+                  f_heads=16, f_dim=128, f_rot=32, f_vdim=128, q_rank=768, kv_rank=96, r_kv_heads=8, f_ff=4096, streams=4),
+    "w4096": dict(width=4096, layers=8, loop=(2, 5, 2), vocab=32768, heads=32, kv_heads=8, dim=128, window=2048, rot=64,
+                  r_heads=32, r_dim=128, r_vdim=256, rank=128, ff=12288,
+                  f_heads=32, f_dim=128, f_rot=32, f_vdim=128, q_rank=1536, kv_rank=96, r_kv_heads=16, f_ff=8192, streams=4),
+}
+
+
+def run_mefupel(args, pk, clocks, windows):
+    """Mefupel at real layer sizes beside Fifudra at equal size (see MEFUPEL_SIZES and run_beside)."""
+    from vllm_cpp_b200.config.fifudra import (DeltaSpec, FifudraConfig, FifudraLayer, FifudraMlp, Hgrn2Spec, LatentAttentionSpec,
+                                              RotarySpec)
+    from vllm_cpp_b200.config.mefupel import (AttentionSpec, GlaSpec, MefupelConfig, MefupelLayer, MefupelMlp, ParallelSpec,
+                                              RetentionSpec, Rotation)
+    context, T = args.context, PREFILL_TOKENS
+
+    def kinds(z):
+        return [("gla", "parallel", "attention")[i % 3] for i in range(z["layers"])]
+
+    def fifudra_kinds(z):
+        return [("delta", "hgrn2", "latent_attention")[i % 3] for i in range(z["layers"])]
+
+    def runs(z, names):
+        a, b, n = z["loop"]
+        return names[:a] + names[a:b] * n + names[b:]
+
+    def configs(z):
+        H, G, d, RH = z["heads"], z["kv_heads"], z["dim"], z["r_heads"]
+        attn = AttentionSpec(heads=H, kv_heads=G, dim=d, vdim=d, scale=d ** -0.5, window=z["window"], rot=Rotation(1e6, d))
+        left = AttentionSpec(heads=H, kv_heads=G, dim=d, vdim=d, scale=d ** -0.5, window=z["window"], rot=Rotation(2e4, z["rot"]))
+        right = RetentionSpec(heads=RH, dim=z["r_dim"], vdim=z["r_vdim"], decay=tuple(1.0 - 2.0 ** (-5 - 6 * i / max(RH - 1, 1)) for i in range(RH)),
+                              rot=Rotation(1e6, z["r_dim"]))
+        mixers = {"gla": GlaSpec(heads=RH, dim=z["r_dim"], vdim=z["r_vdim"], tau=16.0, rank=z["rank"]), "parallel": ParallelSpec(left, right),
+                  "attention": attn}
+        a, b, n = z["loop"]
+        mef = MefupelConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-5, has_loop=True, loop_start=a, loop_stop=b, loop_times=n,
+                            max_positions=context + 4096,
+                            layers=tuple(MefupelLayer(k, mixers[k], MefupelMlp("dense", z["ff"])) for k in kinds(z)))
+        fmix = {"delta": DeltaSpec(heads=RH, kv_heads=z["r_kv_heads"], dim=z["r_dim"], vdim=z["r_vdim"], conv=4),
+                "hgrn2": Hgrn2Spec(heads=RH, dim=z["r_dim"], vdim=z["r_vdim"]),
+                "latent_attention": LatentAttentionSpec(
+                    heads=z["f_heads"], dim=z["f_dim"], rot_dim=z["f_rot"], vdim=z["f_vdim"], q_rank=z["q_rank"], kv_rank=z["kv_rank"],
+                    scale=(z["f_dim"] + z["f_rot"]) ** -0.5, rot=RotarySpec(base=1e6, dims=z["f_rot"]))}
+        fif = FifudraConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-5, embedding_scale=1.0, streams=z["streams"],
+                            loop_start=a, loop_stop=b, loop_times=n, max_positions=context + 4096,
+                            layers=tuple(FifudraLayer(k, fmix[k], FifudraMlp("dense", ff=z["f_ff"])) for k in fifudra_kinds(z)))
+        return {"mefupel": mef, "fifudra": fif}
+
+    def numbers(z, name):
+        W, V = z["width"], z["vocab"]
+        RH, rd, rv = z["r_heads"], z["r_dim"], z["r_vdim"]
+        state_bytes = 2 * 4 * RH * rd * rv              # read and written, 32-bit
+        if name == "fifudra":
+            H, d, r, vd, qr, kr, RG = z["f_heads"], z["f_dim"], z["f_rot"], z["f_vdim"], z["q_rank"], z["kv_rank"], z["r_kv_heads"]
+            order = runs(z, fifudra_kinds(z))
+            n = {k: order.count(k) for k in ("delta", "hgrn2", "latent_attention")}
+            w = {"latent_attention": (qr + kr + r) * W + H * (d + r) * qr + H * d * kr + H * vd * kr + W * H * vd,
+                 "delta": (2 * RG * rd + 2 * RH * rv + 2 * RH) * W + W * RH * rv, "hgrn2": (2 * RH * rd + RH * rv) * W + W * RH * rv}
+            weights = sum(n[k] * w[k] for k in n) + len(order) * 3 * z["f_ff"] * W
+            return dict(weight_bytes=2 * (weights + V * W),
+                        cache_bytes=n["latent_attention"] * (2 * kr + r) * 2 * context + (n["delta"] + n["hgrn2"]) * state_bytes,
+                        prefill_flops=2.0 * T * weights + 2.0 * V * W + n["latent_attention"] * 2.0 * H * (2 * kr + r) * sum(i + 1 for i in range(T))
+                                      + (6.0 * n["delta"] + 4.0 * n["hgrn2"]) * T * RH * rd * rv)
+        H, G, d = z["heads"], z["kv_heads"], z["dim"]
+        order = runs(z, kinds(z))
+        n = {k: order.count(k) for k in ("gla", "parallel", "attention")}
+        attn_w = (H + 2 * G) * d * W + W * H * d
+        left_w = (H + G) * d * W + W * H * d
+        rec_w = (2 * RH * rd + 2 * RH * rv) * W + W * RH * rv
+        w = {"attention": attn_w, "parallel": left_w + rec_w, "gla": rec_w + z["rank"] * (W + RH * rd)}
+        weights = sum(n[k] * w[k] for k in n) + len(order) * 2 * z["ff"] * W
+        keys = min(context, z["window"])
+        seen = sum(min(i + 1, z["window"]) for i in range(T))
+        return dict(weight_bytes=2 * (weights + V * W),
+                    # a cached token: a key row and a value row per KV head, 16-bit
+                    cache_bytes=(n["attention"] + n["parallel"]) * 2 * G * d * 2 * keys + (n["gla"] + n["parallel"]) * state_bytes,
+                    prefill_flops=2.0 * T * weights + 2.0 * V * W + (n["attention"] + n["parallel"]) * 4.0 * H * d * seen
+                                  + 4.0 * (n["gla"] + n["parallel"]) * T * RH * rd * rv)
+
+    return run_beside(args, pk, clocks, windows, "mefupel_beside_fifudra", MEFUPEL_SIZES, configs, numbers)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -721,11 +810,11 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--workloads", default="all", choices=["all", "headline", "14b", "4b", "rimopel", "nagavik", "fifudra"],
+    ap.add_argument("--workloads", default="all", choices=["all", "headline", "14b", "4b", "rimopel", "nagavik", "fifudra", "mefupel"],
                     help="headline: the 8B numbers only; 14b / 4b: that workload alone (prints its own JSON line); rimopel, "
                          "nagavik: that design at real layer sizes beside Qwen3 at equal size, prefill and decode (its own JSON line); "
-                         "fifudra: that design beside Nagavik at equal size, likewise")
-    ap.add_argument("--size", default="", help="rimopel, nagavik, fifudra: one of the workload's sizes only (w2048, w4096; fifudra also w2048_k256)")
+                         "fifudra: that design beside Nagavik at equal size, likewise; mefupel: that design beside Fifudra at equal size, likewise")
+    ap.add_argument("--size", default="", help="rimopel, nagavik, fifudra, mefupel: one of the workload's sizes only (w2048, w4096; fifudra also w2048_k256)")
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profiling runs)")
     ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill"], help="what to run (profiling runs)")
@@ -747,8 +836,8 @@ def main():
     clocks.start()
     windows = []
     try:
-        if args.workloads in ("14b", "4b", "rimopel", "nagavik", "fifudra"):
-            out = {"14b": run_14b, "4b": run_4b, "rimopel": run_rimopel, "nagavik": run_nagavik, "fifudra": run_fifudra}[args.workloads](args, pk, clocks, windows)
+        if args.workloads in ("14b", "4b", "rimopel", "nagavik", "fifudra", "mefupel"):
+            out = {"14b": run_14b, "4b": run_4b, "rimopel": run_rimopel, "nagavik": run_nagavik, "fifudra": run_fifudra, "mefupel": run_mefupel}[args.workloads](args, pk, clocks, windows)
             out["clocks"] = clocks.summary(windows)
             print(json.dumps(out))
             return 0

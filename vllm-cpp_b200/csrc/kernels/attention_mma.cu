@@ -86,10 +86,12 @@ struct AttnArgs {
     const float* dist_b;
     // softcap c > 0: the scaled score becomes c tanh(s / c); slope [nh] (or null): slope_h (pos - j) is taken off it after
     // the cap; sink: a silent key of score 0 without a value in every softmax (it enters as the starting state -- maximum
-    // 0, sum 1 -- of the first key slice's first key group, so slices and groups merge as they are)
+    // 0, or the head's own score sink_value[h], and sum 1 -- of the first key slice's first key group, so slices and groups
+    // merge as they are)
     float softcap;
     const float* slope;
     int sink;
+    const float* sink_value;    // with a sink: the silent key's score per head, not scaled (null: 0)
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
@@ -518,13 +520,15 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
 #pragma unroll
         for (int i = 0; i < ND; ++i) o[mr][i][0] = o[mr][i][1] = o[mr][i][2] = o[mr][i][3] = 0.f;
         const bool with_sink = a.sink != 0 && slice == 0 && wk == 0;
-        m_run[mr][0] = m_run[mr][1] = with_sink ? 0.f : -CUDART_INF_F;
-        l_run[mr][0] = l_run[mr][1] = with_sink && (lane & 3) == 0 ? 1.f : 0.f;   // per-thread partial sums (reduced over the quad at the end)
         r_a[mr] = (wr * MR + mr) * 16 + (lane >> 2);
         pos_a[mr] = pos0 + r_a[mr] / gq;
         pos_b[mr] = pos0 + (r_a[mr] + 8) / gq;
         ok_a[mr] = r_a[mr] < R;
         ok_b[mr] = r_a[mr] + 8 < R;
+        const bool scored = with_sink && a.sink_value != nullptr;
+        m_run[mr][0] = with_sink ? (scored && ok_a[mr] ? a.sink_value[head0 + r_a[mr] % gq] : 0.f) : -CUDART_INF_F;
+        m_run[mr][1] = with_sink ? (scored && ok_b[mr] ? a.sink_value[head0 + (r_a[mr] + 8) % gq] : 0.f) : -CUDART_INF_F;
+        l_run[mr][0] = l_run[mr][1] = with_sink && (lane & 3) == 0 ? 1.f : 0.f;   // per-thread partial sums (reduced over the quad at the end)
     }
     float da_a[MR], db_a[MR], da_b[MR], db_b[MR];   // the distance penalty's a_h ln 2 and b_h of rows a and b
 #pragma unroll
@@ -1099,7 +1103,7 @@ VCB_API int vcb_attn_mma_ex(const void* q, void* out, const void* pages, long lo
                             const int* ctx_len, const int* items, int n_items, int rows_max, float* part_o,
                             float* part_ml, int* slice_counters, const int* dec_rows, int nh, int nkv, int hd,
                             int page_size, int num_pages, int window, float scale, int keep_first, const float* dist_a,
-                            const float* dist_b, float softcap, const float* slope, int sink, int* status, int allow_tma, int cluster, cudaStream_t stream);
+                            const float* dist_b, float softcap, const float* slope, int sink, const float* sink_value, int* status, int allow_tma, int cluster, cudaStream_t stream);
 
 VCB_API int vcb_attn_mma(const void* q, void* out, const void* pages, long long page_stride, const int* block_table,
                          const int* table_row, int max_blocks, const int* q_start, const int* q_len,
@@ -1109,7 +1113,7 @@ VCB_API int vcb_attn_mma(const void* q, void* out, const void* pages, long long 
                          int cluster, cudaStream_t stream) {
     return vcb_attn_mma_ex(q, out, pages, page_stride, block_table, table_row, max_blocks, q_start, q_len, ctx_len, items,
                            n_items, rows_max, part_o, part_ml, slice_counters, dec_rows, nh, nkv, hd, page_size, num_pages,
-                           window, scale, 0, nullptr, nullptr, 0.f, nullptr, 0, status, allow_tma, cluster, stream);
+                           window, scale, 0, nullptr, nullptr, 0.f, nullptr, 0, nullptr, status, allow_tma, cluster, stream);
 }
 
 // keep_first, dist_a, dist_b, softcap, slope, sink: the options described with AttnArgs.
@@ -1118,7 +1122,7 @@ VCB_API int vcb_attn_mma_ex(const void* q, void* out, const void* pages, long lo
                             const int* ctx_len, const int* items, int n_items, int rows_max, float* part_o,
                             float* part_ml, int* slice_counters, const int* dec_rows, int nh, int nkv, int hd,
                             int page_size, int num_pages, int window, float scale, int keep_first, const float* dist_a,
-                            const float* dist_b, float softcap, const float* slope, int sink, int* status, int allow_tma, int cluster, cudaStream_t stream) {
+                            const float* dist_b, float softcap, const float* slope, int sink, const float* sink_value, int* status, int allow_tma, int cluster, cudaStream_t stream) {
     if (n_items == 0) return 0;
     VCB_CHECK_ARG(keep_first >= 0 && (dist_a == nullptr) == (dist_b == nullptr), "attn_mma: bad keep_first %d or half a distance penalty", keep_first);
     VCB_CHECK_ARG(nh > 0 && nkv > 0 && nh % nkv == 0, "attn_mma: %d query heads are not a multiple of %d KV heads", nh, nkv);
@@ -1127,7 +1131,7 @@ VCB_API int vcb_attn_mma_ex(const void* q, void* out, const void* pages, long lo
     VCB_CHECK_ARG(page_size > 0 && window >= 0, "attn_mma: bad page_size %d or window %d", page_size, window);
     AttnArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)pages, page_stride, block_table,
                table_row, max_blocks, q_start, q_len, ctx_len, items, part_o, part_ml, slice_counters, dec_rows, nh, nkv,
-               page_size, num_pages, window, scale, status, FusedQkv{}, cluster, keep_first, dist_a, dist_b, softcap, slope, sink};
+               page_size, num_pages, window, scale, status, FusedQkv{}, cluster, keep_first, dist_a, dist_b, softcap, slope, sink, sink_value};
     VCB_CHECK_ARG(softcap >= 0.f && (dist_a == nullptr || slope == nullptr), "attn_mma: a negative cap, or a logarithmic penalty and a slope at once");
     const bool tma = allow_tma && (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64) &&
                      ((uintptr_t)pages % 16 == 0) && page_stride == (long long)2 * nkv * page_size * hd;

@@ -80,6 +80,7 @@ struct TcArgs {
     float softcap;
     const float* slope;
     int sink;
+    const float* sink_value;    // with a sink: the silent key's score per head, not scaled (null: 0)
 };
 
 // a box of whole groups of 8 tokens, all lanes: coordinates (lane 0, token 0, half 0, group)
@@ -602,6 +603,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
             // a cap on the scaled score and a slope times the distance, likewise brought to the base-2 domain here
             const bool lin = OPT && (a.slope != nullptr || a.softcap > 0.f);
             const bool sink = OPT && a.sink != 0;
+            const float sink_l2 = sink && a.sink_value != nullptr && row_ok ? a.sink_value[u.head0 + ih] * LOG2E : 0.f;
             const float slope_l2 = lin && a.slope != nullptr && row_ok ? a.slope[u.head0 + ih] * LOG2E : 0.f;
             const float cap_l2 = a.softcap * LOG2E, cap_in = a.softcap > 0.f ? 2.f * scale_log2 / a.softcap : 0.f;
             const float sl2 = penal || lin ? 1.f : scale_log2;   // what is left to multiply the scores by on their way to weights
@@ -672,7 +674,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                     mx4[(c >> 1) & 3] = max3(mx4[(c >> 1) & 3], __uint_as_float(sv[c / 16][c % 16]), __uint_as_float(sv[c / 16][c % 16 + 1]));
                 // the scale is positive: the maximum of the scaled scores is the scaled maximum
                 float m_new = fmaxf(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2, m_ref);
-                if (sink && j == 0) m_new = fmaxf(m_new, 0.f);   // the silent key of score 0 joins the row's first tile
+                if (sink && j == 0) m_new = fmaxf(m_new, sink_l2);   // the silent key (of score 0, or the head's own) joins the row's first tile
                 // Move the reference when the maximum has outgrown it.  O (in TMEM) holds the sum so far against the
                 // old reference: the warp rescales its 32 rows together, rows that keep theirs by a factor of one.
                 const bool first_keys = m_ref == -CUDART_INF_F && m_new != -CUDART_INF_F;   // nothing summed yet
@@ -698,7 +700,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                     l_run *= alpha;
                 }
                 if (grow || first_keys) m_ref = m_new;
-                if (sink && j == 0) l_run = exp2f(-m_ref);       // its weight against the reference (no value to add)
+                if (sink && j == 0) l_run = exp2f(sink_l2 - m_ref);       // its weight against the reference (no value to add)
                 const float m_sub = m_ref == -CUDART_INF_F ? 0.f : m_ref;   // no key yet: every weight is exp2(-inf) = 0
 
                 uint64_t sum4[4] = {0ull, 0ull, 0ull, 0ull};   // four pairs of partial sums, all +0
@@ -826,7 +828,7 @@ VCB_API int vcb_attn_tc_supported(int dtype, int hd, int page_size) {
 VCB_API int vcb_attn_tc_ex(const void* q, void* out, const void* pages, long long page_stride, const int* block_table,
                            const int* table_row, int max_blocks, const int* q_start, const int* q_len, const int* ctx_len,
                            const int* items, int n_items, int nh, int nkv, int hd, int page_size, int num_pages, int window,
-                           float scale, int keep_first, const float* dist_a, const float* dist_b, float softcap, const float* slope, int sink, int* status, int* work,
+                           float scale, int keep_first, const float* dist_a, const float* dist_b, float softcap, const float* slope, int sink, const float* sink_value, int* status, int* work,
                            cudaStream_t stream);
 
 // Prompt portions only: every item has slice 0 of 1 and at most 128 rows (tokens x query heads per KV head).
@@ -837,13 +839,13 @@ VCB_API int vcb_attn_tc(const void* q, void* out, const void* pages, long long p
                         const int* items, int n_items, int nh, int nkv, int hd, int page_size, int num_pages, int window,
                         float scale, int* status, int* work, cudaStream_t stream) {
     return vcb_attn_tc_ex(q, out, pages, page_stride, block_table, table_row, max_blocks, q_start, q_len, ctx_len, items, n_items,
-                          nh, nkv, hd, page_size, num_pages, window, scale, 0, nullptr, nullptr, 0.f, nullptr, 0, status, work, stream);
+                          nh, nkv, hd, page_size, num_pages, window, scale, 0, nullptr, nullptr, 0.f, nullptr, 0, nullptr, status, work, stream);
 }
 
 VCB_API int vcb_attn_tc_ex(const void* q, void* out, const void* pages, long long page_stride, const int* block_table,
                            const int* table_row, int max_blocks, const int* q_start, const int* q_len, const int* ctx_len,
                            const int* items, int n_items, int nh, int nkv, int hd, int page_size, int num_pages, int window,
-                           float scale, int keep_first, const float* dist_a, const float* dist_b, float softcap, const float* slope, int sink, int* status, int* work,
+                           float scale, int keep_first, const float* dist_a, const float* dist_b, float softcap, const float* slope, int sink, const float* sink_value, int* status, int* work,
                            cudaStream_t stream) {
     if (n_items == 0) return 0;
     VCB_CHECK_ARG(keep_first >= 0 && (dist_a == nullptr) == (dist_b == nullptr), "attn_tc: bad keep_first %d or half a distance penalty", keep_first);
@@ -860,7 +862,7 @@ VCB_API int vcb_attn_tc_ex(const void* q, void* out, const void* pages, long lon
     const int g = nh / nkv;
     const int hchunks = (g + ROWS - 1) / ROWS;
     TcArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, block_table, table_row, max_blocks, q_start, q_len, ctx_len,
-             items, nh, nkv, page_size, num_pages, window, scale, status, n_items * nkv * hchunks, work, keep_first, dist_a, dist_b, softcap, slope, sink};
+             items, nh, nkv, page_size, num_pages, window, scale, status, n_items * nkv * hchunks, work, keep_first, dist_a, dist_b, softcap, slope, sink, sink_value};
     VCB_CHECK_ARG(softcap >= 0.f && (dist_a == nullptr || slope == nullptr), "attn_tc: a negative cap, or a logarithmic penalty and a slope at once");
     if (keep_first > 0 || dist_a != nullptr || softcap > 0.f || slope != nullptr || sink) return hd == 64 ? launch<64, true>(map, a, n_items, stream) : launch<128, true>(map, a, n_items, stream);
     return hd == 64 ? launch<64, false>(map, a, n_items, stream) : launch<128, false>(map, a, n_items, stream);

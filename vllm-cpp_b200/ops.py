@@ -107,14 +107,14 @@ def _declare(L):
         "vcb_selftest_wait_timeout": [LL, P, P, P],
         "vcb_state_reset": [P, I, LL, LL, LL, I, I, P, P, P, I, ctypes.c_uint, P, P],
         "vcb_attn_mma": [P, P, P, LL, P, P, I, P, P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, F, P, I, I, P],
-        "vcb_attn_mma_ex": [P, P, P, LL, P, P, I, P, P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, F, I, P, P, F, P, I, P, I, I, P],
+        "vcb_attn_mma_ex": [P, P, P, LL, P, P, I, P, P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, F, I, P, P, F, P, I, P, P, I, I, P],
         "vcb_attn_mma_supported": [I, I],
         "vcb_attn_mma_max_clusters": [I, I, I],
         "vcb_attn_mma_fused_supported": [I, I, I],
         "vcb_attn_mma_decode_fused": [P, I, LL, P, P, I, I, F, P, I, P, P, P, LL, P, P, I, P, P, P, P, I, P, P, P, P, I, I,
                                       I, I, I, I, F, P, I, P],
         "vcb_attn_tc": [P, P, P, LL, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, P, P, P],
-        "vcb_attn_tc_ex": [P, P, P, LL, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P, F, P, I, P, P, P],
+        "vcb_attn_tc_ex": [P, P, P, LL, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P, F, P, I, P, P, P, P],
         "vcb_attn_tc_supported": [I, I, I],
         "vcb_attn_stream": [P, P, P, LL, P, P, I, P, P, P, I, P, I, I, I, I, I, I, F, P, I, P],
         "vcb_attn_stream_supported": [I, I, I, I, I],
@@ -407,6 +407,15 @@ def attn_paged(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_ite
     _call("vcb_attn_paged", _p(q), _p(out), _dt(q), _p(pages), pages.stride(0), _p(block_table), _p(table_row), block_table.shape[1],
           _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items, rows_max, _p(part_o), _p(part_ml), nh, nkv, hd,
           page_size, num_pages, int(window or 0), 1.0 / math.sqrt(hd), _p(status), _stream())
+
+
+def _sink_scores(sink, nh):
+    """``sink`` as the attention wrappers take it (False, True, or a float32 tensor [nh] of scores) -> the tensor or None."""
+    if not torch.is_tensor(sink):
+        return None
+    _need(sink, "sink", torch.float32)
+    assert sink.numel() == nh
+    return sink
 
 
 def kv_page_views(pages, nkv, hd, hd_v):
@@ -920,6 +929,7 @@ def attn_tc(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items,
     if work is None:
         work = torch.zeros(2, dtype=torch.int32, device=q.device)
     _need(work, "work", torch.int32)
+    sink_value = _sink_scores(sink, nh)
     _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(pages, "pages", torch.bfloat16)
     for name, t in (("block_table", block_table), ("q_start", q_start), ("q_len", q_len), ("ctx_len", ctx_len),
                     ("items", items)):
@@ -934,7 +944,8 @@ def attn_tc(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items,
     _call("vcb_attn_tc_ex", _p(q), _p(out), _p(pages), pages.stride(0), _p(block_table), _p(table_row),
           block_table.shape[1], _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items, nh, nkv, hd, page_size,
           num_pages, int(window or 0), 1.0 / math.sqrt(hd) if scale is None else float(scale), int(keep_first or 0),
-          _p(dist_a), _p(dist_b), float(softcap or 0.0), _p(slope), int(bool(sink)), _p(status), _p(work), _stream())
+          _p(dist_a), _p(dist_b), float(softcap or 0.0), _p(slope), int(sink_value is not None or bool(sink)), _p(sink_value),
+          _p(status), _p(work), _stream())
 
 
 def attn_mma(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items, rows_max, part_o, part_ml,
@@ -946,6 +957,7 @@ def attn_mma(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items
     With ``slice_counters`` (int32 zeros, one per decoded token and KV head group, left at zero again) and
     ``dec_rows``, the block that finishes a token's last key slice merges the slices itself; with ``cluster`` = the
     number of slices per token (2 to 8) as well, the slices' blocks run as a cluster and merge through shared memory."""
+    sink_value = _sink_scores(sink, nh)
     _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(pages, "pages", torch.bfloat16)
     for name, t in (("block_table", block_table), ("q_start", q_start), ("q_len", q_len), ("ctx_len", ctx_len),
                     ("items", items)):
@@ -961,7 +973,8 @@ def attn_mma(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items
           block_table.shape[1], _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items, rows_max, _p(part_o),
           _p(part_ml), _p(slice_counters), _p(dec_rows), nh, nkv, hd, page_size, num_pages, int(window or 0),
           1.0 / math.sqrt(hd) if scale is None else float(scale), int(keep_first or 0), _p(dist_a), _p(dist_b),
-          float(softcap or 0.0), _p(slope), int(bool(sink)), _p(status), int(allow_tma), int(cluster), _stream())
+          float(softcap or 0.0), _p(slope), int(sink_value is not None or bool(sink)), _p(sink_value), _p(status), int(allow_tma),
+          int(cluster), _stream())
 
 
 def attn_stream_supported(dtype: torch.dtype, hd: int, page_size: int, nh: int, nkv: int) -> bool:

@@ -44,7 +44,7 @@ MMA_ATTENTION = os.environ.get("VLLM_CPP_B200_WINDOW_ATTN_MMA", "1") != "0"
 # whether the tensor-core kernels take the cap, the slope and the sink (else steps with them run on the plain kernel)
 EXTRAS_ON_TENSOR_CORES = True
 # whether they take a sink with a learned score per head (else such steps run on the plain kernel)
-SINK_SCORES_ON_TENSOR_CORES = False
+SINK_SCORES_ON_TENSOR_CORES = True
 
 
 def paged_attention(ctx, kv, q, out, *, nh, nkv, hd, vd, scale, window=0, keep_first=0, dist_a=None, dist_b=None,
