@@ -294,7 +294,8 @@ TOL16 = dict(atol=3e-2, rtol=2e-2)
 
 @gpu
 @pytest.mark.parametrize("W,n_terms,S,out_dtype", [(6, 1, 1, torch.float32), (50, 2, 2, torch.bfloat16), (320, 2, 3, torch.float32),
-                                                   (2500, 4, 1, torch.bfloat16), (64, 0, 1, torch.float32), (13000, 1, 2, torch.float32)])
+                                                   (2500, 4, 1, torch.bfloat16), (64, 0, 1, torch.float32), (13000, 1, 2, torch.float32),
+                                                   (12288, 2, 1, torch.bfloat16)])
 def test_pending_results_are_added_and_normed_in_one_pass(W, n_terms, S, out_dtype):
     from vllm_cpp_b200 import ops
     g = torch.Generator().manual_seed(W + n_terms)
@@ -325,7 +326,7 @@ def test_pending_results_are_added_and_normed_in_one_pass(W, n_terms, S, out_dty
 
 
 @gpu
-@pytest.mark.parametrize("W,n,S", [(6, 2, 1), (50, 2, 2), (192, 1, 3), (1000, 3, 1), (4096, 2, 2), (77, 4, 1)])
+@pytest.mark.parametrize("W,n,S", [(6, 2, 1), (50, 2, 2), (192, 1, 3), (1000, 3, 1), (4096, 2, 2), (77, 4, 1), (6144, 2, 1)])
 def test_results_of_mixers_side_by_side_are_normed_and_averaged(W, n, S):
     from vllm_cpp_b200 import ops
     g = torch.Generator().manual_seed(W * n)
@@ -340,7 +341,7 @@ def test_results_of_mixers_side_by_side_are_normed_and_averaged(W, n, S):
 
 @gpu
 @pytest.mark.parametrize("F,S,dtype", [(5, 1, torch.float32), (40, 2, torch.bfloat16), (256, 1, torch.float32), (3000, 3, torch.float32),
-                                       (14336, 1, torch.bfloat16)])
+                                       (14336, 1, torch.bfloat16), (12288, 1, torch.bfloat16)])
 def test_normed_polynomial_activation(F, S, dtype):
     from vllm_cpp_b200 import ops
     g = torch.Generator().manual_seed(F)

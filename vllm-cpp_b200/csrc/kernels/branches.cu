@@ -77,6 +77,33 @@ __device__ __forceinline__ void store_out(void* out, int dtype, size_t at, const
     } else ((__nv_bfloat16*)out)[at] = __float2bfloat16_rn(y.v[0]);
 }
 
+// N sums over the block in one round of barriers; every thread gets them all.  The order of the additions depends only
+// on the block size.
+template <int N>
+__device__ __forceinline__ void block_sums(float (&v)[N], float* scratch /* >= N * 33 floats */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int k = 0; k < N; ++k) v[k] = warp_sum(v[k]);
+    __syncthreads();
+    if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < N; ++k) scratch[k * 33 + warp] = v[k];
+    }
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+            float t = lane < nwarps ? scratch[k * 33 + lane] : 0.f;
+            t = warp_sum(t);
+            if (lane == 0) scratch[k * 33 + 32] = t;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < N; ++k) v[k] = scratch[k * 33 + 32];
+}
+
 template <int V>
 __global__ void sum_add_rmsnorm_kernel(SumArgs a) {
     extern __shared__ __align__(16) float row_s[];      // [H]
@@ -133,26 +160,31 @@ struct BranchArgs {
 template <int V>
 __global__ void branch_norm_mean_kernel(BranchArgs a) {
     extern __shared__ __align__(16) float row_s[];      // [n][H]
-    __shared__ float red[33];
+    __shared__ float red[MAX_TERMS * 33];
     pdl_trigger();
     pdl_wait();
     const size_t t = blockIdx.x;
     const int H = a.H;
     float inv[MAX_TERMS];
-    for (int b = 0; b < a.n; ++b) {
-        float ss = 0.f;
-        for (int c = threadIdx.x * V; c < H; c += blockDim.x * V) {
-            Pack<V> x;
 #pragma unroll
-            for (int j = 0; j < V; ++j) x.v[j] = 0.f;
-            add_rows<V>(x, a.y[b], t, c);
+    for (int b = 0; b < MAX_TERMS; ++b) inv[b] = 0.f;
+    for (int c = threadIdx.x * V; c < H; c += blockDim.x * V) {
 #pragma unroll
-            for (int j = 0; j < V; ++j) ss = fmaf(x.v[j], x.v[j], ss);
-            x.store(row_s + (size_t)b * H + c);
+        for (int b = 0; b < MAX_TERMS; ++b) {
+            if (b < a.n) {
+                Pack<V> x;
+#pragma unroll
+                for (int j = 0; j < V; ++j) x.v[j] = 0.f;
+                add_rows<V>(x, a.y[b], t, c);
+#pragma unroll
+                for (int j = 0; j < V; ++j) inv[b] = fmaf(x.v[j], x.v[j], inv[b]);
+                x.store(row_s + (size_t)b * H + c);
+            }
         }
-        ss = block_sum(ss, red);
-        inv[b] = 1.0f / sqrtf(ss / (float)H + a.eps);
     }
+    block_sums<MAX_TERMS>(inv, red);
+#pragma unroll
+    for (int b = 0; b < MAX_TERMS; ++b) inv[b] = 1.0f / sqrtf(inv[b] / (float)H + a.eps);
     const float share = 1.0f / (float)a.n;
     for (int c = threadIdx.x * V; c < H; c += blockDim.x * V) {
         Pack<V> acc;
@@ -163,7 +195,7 @@ __global__ void branch_norm_mean_kernel(BranchArgs a) {
             x.load(row_s + (size_t)b * H + c);
             g.load(a.gain[b] + c);
 #pragma unroll
-            for (int j = 0; j < V; ++j) acc.v[j] += x.v[j] * inv[b] * g.v[j];
+            for (int j = 0; j < V; ++j) acc.v[j] += x.v[j] * (b == 0 ? inv[0] : b == 1 ? inv[1] : b == 2 ? inv[2] : inv[3]) * g.v[j];
         }
 #pragma unroll
         for (int j = 0; j < V; ++j) acc.v[j] *= share;
@@ -174,7 +206,7 @@ __global__ void branch_norm_mean_kernel(BranchArgs a) {
 template <int V>
 __global__ void polynorm_kernel(Rows u, const float* __restrict__ coef, float eps, void* out, int out_dtype, int F) {
     extern __shared__ __align__(16) float row_s[];      // [F]
-    __shared__ float red[33];
+    __shared__ float red[3 * 33];
     pdl_trigger();
     pdl_wait();
     const size_t t = blockIdx.x;
@@ -193,9 +225,11 @@ __global__ void polynorm_kernel(Rows u, const float* __restrict__ coef, float ep
         }
         z.store(row_s + c);
     }
-    s2 = block_sum(s2, red);
-    s4 = block_sum(s4, red);
-    s6 = block_sum(s6, red);
+    float sums[3] = {s2, s4, s6};
+    block_sums<3>(sums, red);
+    s2 = sums[0];
+    s4 = sums[1];
+    s6 = sums[2];
     const float a = coef[0], b = coef[1], cc = coef[2], e = coef[3];
     const float r1 = a / sqrtf(s2 / (float)F + eps), r2 = b / sqrtf(s4 / (float)F + eps), r3 = cc / sqrtf(s6 / (float)F + eps);
     for (int c = threadIdx.x * V; c < F; c += blockDim.x * V) {
@@ -215,7 +249,7 @@ bool rows_vec_ok(const Rows& r) { return ((uintptr_t)r.p % 16 == 0) && r.ld % 4 
 int block_for(int width, int v) {
     const int lanes = (width + v - 1) / v;
     int t = 128;
-    while (t < lanes && t < 1024) t <<= 1;
+    while (t < lanes && t < 512) t <<= 1;      // (two or more blocks an SM: they hide one another's round trips)
     return t;
 }
 
@@ -225,7 +259,8 @@ int want_smem(K kern, size_t smem, const char* name) {
         vcb_set_error("%s: a row of %zu bytes is more than the kernel's shared memory holds", name, smem);
         return -1;
     }
-    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    // (the kernels hold a few static words beside the row)
+    if (smem + 1024 > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         vcb_set_error("%s: %zu bytes of shared memory refused", name, smem);
         return -2;
     }

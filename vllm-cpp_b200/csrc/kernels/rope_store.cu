@@ -193,7 +193,7 @@ VCB_API int vcb_qkv_rope_store(const float* qkv, int S, long long s_stride, long
     const size_t smem = (size_t)(nh * hd + nkv * hd + (v_from_k ? 0 : nkv * vd) + rot + (vfreq ? vrot : 0)) * sizeof(float);
     VCB_CHECK_ARG(smem <= 200 * 1024, "qkv_rope_store: a token's %zu bytes are more than the kernel's shared memory holds", smem);
     auto kern = dtype == VCB_F32 ? qkv_rope_store_kernel<float> : qkv_rope_store_kernel<__nv_bfloat16>;
-    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    if (smem + 1024 > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         vcb_set_error("qkv_rope_store: %zu bytes of shared memory refused", smem);
         return -2;
     }
