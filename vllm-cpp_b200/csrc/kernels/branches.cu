@@ -105,7 +105,7 @@ __device__ __forceinline__ void block_sums(float (&v)[N], float* scratch /* >= N
 }
 
 template <int V>
-__global__ void sum_add_rmsnorm_kernel(SumArgs a) {
+__global__ __launch_bounds__(512, 3) void sum_add_rmsnorm_kernel(SumArgs a) {
     extern __shared__ __align__(16) float row_s[];      // [H]
     __shared__ float red[33];
     pdl_trigger();
@@ -158,7 +158,7 @@ struct BranchArgs {
 };
 
 template <int V>
-__global__ void branch_norm_mean_kernel(BranchArgs a) {
+__global__ __launch_bounds__(512, 3) void branch_norm_mean_kernel(BranchArgs a) {
     extern __shared__ __align__(16) float row_s[];      // [n][H]
     __shared__ float red[MAX_TERMS * 33];
     pdl_trigger();
@@ -204,7 +204,7 @@ __global__ void branch_norm_mean_kernel(BranchArgs a) {
 }
 
 template <int V>
-__global__ void polynorm_kernel(Rows u, const float* __restrict__ coef, float eps, void* out, int out_dtype, int F) {
+__global__ __launch_bounds__(512, 3) void polynorm_kernel(Rows u, const float* __restrict__ coef, float eps, void* out, int out_dtype, int F) {
     extern __shared__ __align__(16) float row_s[];      // [F]
     __shared__ float red[3 * 33];
     pdl_trigger();
