@@ -746,7 +746,7 @@ def run_mefupel(args, pk, clocks, windows):
     def configs(z):
         H, G, d, RH = z["heads"], z["kv_heads"], z["dim"], z["r_heads"]
         attn = AttentionSpec(heads=H, kv_heads=G, dim=d, vdim=d, scale=d ** -0.5, window=z["window"], rot=Rotation(1e6, d))
-        left = AttentionSpec(heads=H, kv_heads=G, dim=d, vdim=d, scale=d ** -0.5, window=z["window"], rot=Rotation(2e4, z["rot"]))
+        left = AttentionSpec(heads=H, kv_heads=G, dim=d, vdim=d, scale=d ** -0.5, window=z["window"], rot=Rotation(5e5, z["rot"]))
         right = RetentionSpec(heads=RH, dim=z["r_dim"], vdim=z["r_vdim"], decay=tuple(1.0 - 2.0 ** (-5 - 6 * i / max(RH - 1, 1)) for i in range(RH)),
                               rot=Rotation(1e6, z["r_dim"]))
         mixers = {"gla": GlaSpec(heads=RH, dim=z["r_dim"], vdim=z["r_vdim"], tau=16.0, rank=z["rank"]), "parallel": ParallelSpec(left, right),
